@@ -1,0 +1,164 @@
+/*
+ * knlp_b200 — C ABI of the B200 (sm_100a) packed-KV-cache hot path.
+ *
+ * Three device operations and their helpers:
+ *   quant_append   quantize new K/V tokens and scatter them into the paged cache
+ *   decode_splitk  split-context GQA decode attention over the packed cache,
+ *                  emitting (m, l, o) softmax partials per (sequence, q head, split)
+ *   combine        merge partials into the attention output (or into one partial)
+ *
+ * Every entry point is plain C: raw device pointers, sizes, strides and a
+ * cudaStream_t passed as void*.  Nothing here allocates or synchronises except
+ * where a comment says so; all launches go to the given stream, so the calls are
+ * stream-ordered and capturable.  Return value: 0 on success, a negative
+ * knlp_status on an argument error detected on the host before any launch.
+ *
+ * Reference interfaces replaced (mcgrof/knlp, fused-quant/fused_int4.v0.1.0.py):
+ *   reshape_and_cache_int4          :418-472   -> knlp_b200_quant_append
+ *   reshape_and_cache_v_only_int4   :603-647   -> knlp_b200_quant_append (K plane NULL)
+ *   reshape_and_cache_k_int8        :1287-1312 -> knlp_b200_quant_append (K mode INT8_G32)
+ *   fused_int4_decode               :901-979   -> knlp_b200_decode_splitk + knlp_b200_combine
+ *   kint8_vint4_decode              :1496-1554 -> same, K mode INT8_G32
+ * Cache layouts are the reference's (:213-223): codes [num_blocks, block_size,
+ * num_kv_heads, head_size/2] uint8 (INT4; element 2j in the low nibble of byte j)
+ * or [.., head_size] int8 (INT8); scales and zeros [.., head_size/32] fp16.
+ */
+#ifndef KNLP_B200_H_
+#define KNLP_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KNLP_B200_ABI_VERSION 1
+#define KNLP_GROUP_SIZE 32
+
+typedef enum {
+  KNLP_OK = 0,
+  KNLP_ERR_NULL = -1,       /* a required pointer is NULL */
+  KNLP_ERR_SHAPE = -2,      /* unsupported head_dim / head counts / sizes */
+  KNLP_ERR_DTYPE = -3,      /* unknown dtype code */
+  KNLP_ERR_MODE = -4,       /* unknown or unsupported K/V mode combination */
+  KNLP_ERR_STRIDE = -5,     /* stride or alignment the kernels cannot address */
+  KNLP_ERR_WORKSPACE = -6,  /* n_splits / workspace arguments out of range */
+  KNLP_ERR_LAUNCH = -7,     /* the CUDA runtime refused the launch */
+  KNLP_ERR_NO_DEVICE = -8,  /* no usable sm_100 device / kernel image */
+  KNLP_ERR_TOO_LARGE = -9   /* request exceeds a fixed capacity (see the entry point) */
+} knlp_status;
+
+typedef enum { KNLP_F32 = 0, KNLP_F16 = 1, KNLP_BF16 = 2 } knlp_dtype;
+
+typedef enum {
+  KNLP_KV_NONE = 0,      /* plane absent (skip) */
+  KNLP_KV_INT4_SYM = 1,  /* offset-binary nibbles, scale only (reference :328-357) */
+  KNLP_KV_INT4_ASYM = 2, /* unsigned nibbles, scale + zero (reference :308-327) */
+  KNLP_KV_INT8_G32 = 3   /* int8 codes, per-group-32 scale (reference :1270-1284) */
+} knlp_kv_mode;
+
+/* One cache plane (K or V).  Strides are in ELEMENTS of the array they index
+ * (bytes for codes, fp16 elements for scales/zeros), for the three outer
+ * dimensions: [0] physical block, [1] token within the block, [2] kv head.
+ * The innermost dimension must be contiguous. */
+typedef struct {
+  void* codes;
+  void* scales;
+  void* zeros; /* NULL unless mode == KNLP_KV_INT4_ASYM */
+  int64_t codes_stride[3];
+  int64_t scales_stride[3];
+  int64_t zeros_stride[3];
+  int32_t mode; /* knlp_kv_mode */
+  int32_t reserved;
+} knlp_kv_plane;
+
+/* Flags for knlp_b200_decode_splitk. */
+#define KNLP_DECODE_FORCE_GENERIC 1u /* use the stride-generic CUDA-core kernel */
+
+/* ABI version of the loaded library (KNLP_B200_ABI_VERSION at build time). */
+int knlp_b200_abi_version(void);
+
+/* Static description of a knlp_status. */
+const char* knlp_b200_strerror(int status);
+
+/*
+ * Quantize n_tokens new tokens and write them into the paged cache.
+ * Replaces reshape_and_cache_int4 / _v_only_int4 / _k_int8 (see file header).
+ *   key, value        [n_tokens, n_kv_heads, head_dim] of src_dtype; stride arrays give
+ *                     the token and head strides in elements.  A NULL tensor or a NULL /
+ *                     KNLP_KV_NONE plane skips that side.
+ *   slot_mapping      int64 [n_tokens]; slot < 0 skips the token (reference :266-268);
+ *                     block = slot / block_size, offset = slot % block_size.
+ *   clip_ratio        outlier clip of the symmetric INT4 mode (reference :336-347);
+ *                     <= 0 disables it.  Ignored by the other modes.
+ * Arithmetic is IEEE fp32 with true division and round-half-away-from-zero, so
+ * packed bytes, scales and zeros are bit-identical to the reference's.
+ */
+int knlp_b200_quant_append(const void* key, const int64_t key_stride[2],
+                           const void* value, const int64_t value_stride[2],
+                           int src_dtype,
+                           const knlp_kv_plane* k_plane, const knlp_kv_plane* v_plane,
+                           const int64_t* slot_mapping,
+                           int n_tokens, int n_kv_heads, int head_dim, int block_size,
+                           float clip_ratio, void* stream);
+
+/*
+ * Recommend a split count for decode_splitk and report the workspace it needs.
+ * Pure host arithmetic (queries the SM count of the current device once).
+ *   n_splits_out          splits per sequence to pass to decode_splitk
+ *   workspace_floats_out  floats needed for part_m + part_l + part_o together:
+ *                         n_seqs * n_q_heads * n_splits * (head_dim + 2)
+ */
+int knlp_b200_decode_plan(int n_seqs, int n_q_heads, int n_kv_heads, int head_dim,
+                          int block_size, int max_seq_len, int k_mode, int v_mode,
+                          int* n_splits_out, int64_t* workspace_floats_out);
+
+/*
+ * Split-context decode attention over the packed cache.  Replaces the kernel
+ * launch of fused_int4_decode / kint8_vint4_decode (see file header).
+ *   query        [n_seqs, n_q_heads, head_dim] of q_dtype; q_stride = {seq, head} in elements
+ *   block_table  int32 [n_seqs, *]; row stride bt_stride; entry i of a row is the
+ *                physical block of tokens [i*block_size, (i+1)*block_size)
+ *   seq_lens     int32 [n_seqs]; number of cached tokens to attend to (0 allowed)
+ *   num_blocks   physical blocks in the cache; table entries are clamped to
+ *                [0, num_blocks) before use, so a corrupt table cannot fault
+ *   n_splits     >= 1.  Split i of a sequence covers tokens
+ *                [i*chunk, min((i+1)*chunk, seq_len)), chunk = ceil(max_seq_len/n_splits)
+ *                rounded up to a multiple of 64
+ *   max_seq_len  upper bound of seq_lens known on the host (sizes the splits)
+ *   part_m/l     float [n_seqs, n_q_heads, n_splits]   running max (natural-log domain,
+ *                of the scaled scores) and sum of exp(s - m); empty split: -inf, 0
+ *   part_o       float [n_seqs, n_q_heads, n_splits, head_dim]  UN-normalised sum p*v
+ * The softmax scale is head_dim^-1/2, applied after the dot product (reference :805).
+ */
+int knlp_b200_decode_splitk(const void* query, int q_dtype, const int64_t q_stride[2],
+                            const knlp_kv_plane* k_plane, const knlp_kv_plane* v_plane,
+                            const int32_t* block_table, int64_t bt_stride,
+                            const int32_t* seq_lens, int64_t num_blocks,
+                            int n_seqs, int n_q_heads, int n_kv_heads, int head_dim,
+                            int block_size, int n_splits, int max_seq_len,
+                            float* part_m, float* part_l, float* part_o,
+                            unsigned flags, void* stream);
+
+/*
+ * Merge n_parts partials per (sequence, q head) row.  No counterpart function
+ * in the reference: the algebra is its in-loop online-softmax recurrence
+ * (:808-815, :883-887) applied across splits.
+ *   part_m/l     element (row, p) at row*ml_row_stride + p*ml_part_stride
+ *   part_o       element (row, p, :) at row*o_row_stride + p*o_part_stride
+ *   out          [n_rows, head_dim] with row stride out_row_stride (elements) of
+ *                out_dtype: normalised attention output; rows with no tokens give 0
+ *   out_m/out_l  if both non-NULL, the merged partial is emitted instead: out
+ *                (must be KNLP_F32) receives the UN-normalised o, out_m/out_l [n_rows]
+ */
+int knlp_b200_combine(const float* part_m, const float* part_l, const float* part_o,
+                      int n_parts, int64_t ml_row_stride, int64_t ml_part_stride,
+                      int64_t o_row_stride, int64_t o_part_stride,
+                      void* out, int out_dtype, int64_t out_row_stride,
+                      float* out_m, float* out_l,
+                      int n_rows, int head_dim, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KNLP_B200_H_ */

@@ -1,0 +1,111 @@
+// Shared device/host definitions for the packed-KV kernels (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/knlp_b200.h"
+
+namespace knlp {
+
+constexpr int kGroup = KNLP_GROUP_SIZE;  // elements per scale/zero group
+
+// Device-side view of one cache plane; mirrors knlp_kv_plane.
+struct Plane {
+  uint8_t* codes;
+  __half* scales;
+  __half* zeros;
+  int64_t cs[3];  // codes strides: block, token, head (bytes)
+  int64_t ss[3];  // scales strides (fp16 elements)
+  int64_t zs[3];  // zeros strides
+  int mode;
+};
+
+inline Plane make_plane(const knlp_kv_plane* p) {
+  Plane d{};
+  if (!p) {
+    d.mode = KNLP_KV_NONE;
+    return d;
+  }
+  d.codes = static_cast<uint8_t*>(p->codes);
+  d.scales = static_cast<__half*>(p->scales);
+  d.zeros = static_cast<__half*>(p->zeros);
+  for (int i = 0; i < 3; ++i) {
+    d.cs[i] = p->codes_stride[i];
+    d.ss[i] = p->scales_stride[i];
+    d.zs[i] = p->zeros ? p->zeros_stride[i] : 0;
+  }
+  d.mode = p->mode;
+  return d;
+}
+
+// Exact widening load of one source element.
+template <int DT>
+__device__ __forceinline__ float load_elem(const void* base, int64_t idx) {
+  if constexpr (DT == KNLP_F32) {
+    return static_cast<const float*>(base)[idx];
+  } else if constexpr (DT == KNLP_F16) {
+    return __half2float(static_cast<const __half*>(base)[idx]);
+  } else {
+    return __bfloat162float(static_cast<const __nv_bfloat16*>(base)[idx]);
+  }
+}
+
+__device__ __forceinline__ float load_elem_rt(const void* base, int64_t idx, int dt) {
+  if (dt == KNLP_F32) return load_elem<KNLP_F32>(base, idx);
+  if (dt == KNLP_F16) return load_elem<KNLP_F16>(base, idx);
+  return load_elem<KNLP_BF16>(base, idx);
+}
+
+__device__ __forceinline__ void store_elem_rt(void* base, int64_t idx, float v, int dt) {
+  if (dt == KNLP_F32) {
+    static_cast<float*>(base)[idx] = v;
+  } else if (dt == KNLP_F16) {
+    static_cast<__half*>(base)[idx] = __float2half_rn(v);
+  } else {
+    static_cast<__nv_bfloat16*>(base)[idx] = __float2bfloat16_rn(v);
+  }
+}
+
+// Split length used by decode_splitk: ceil(max_len / n_splits) rounded up to 64.
+__host__ __device__ inline int split_chunk(int max_len, int n_splits) {
+  int c = (max_len + n_splits - 1) / n_splits;
+  c = (c + 63) / 64 * 64;
+  return c < 64 ? 64 : c;
+}
+
+// Host-side launch functions implemented in the individual .cu files.
+int launch_quant_append(const void* key, const int64_t* kstride, const void* value,
+                        const int64_t* vstride, int src_dtype, const Plane& kp, const Plane& vp,
+                        const int64_t* slot_mapping, int n_tokens, int n_kv_heads, int head_dim,
+                        int block_size, float clip_ratio, cudaStream_t st);
+
+struct DecodeArgs {
+  const void* q;
+  int q_dtype;
+  int64_t q_stride[2];
+  Plane k, v;
+  const int32_t* block_table;
+  int64_t bt_stride;
+  const int32_t* seq_lens;
+  int64_t num_blocks;
+  int n_seqs, n_q_heads, n_kv_heads, head_dim, block_size;
+  int n_splits, chunk;
+  float* part_m;
+  float* part_l;
+  float* part_o;
+};
+
+int launch_decode_generic(const DecodeArgs& a, cudaStream_t st);
+// Returns KNLP_OK if it launched, 1 if the shape/strides are not eligible for the
+// tensor-core kernel (caller falls back to the generic one), <0 on error.
+int launch_decode_mma(const DecodeArgs& a, cudaStream_t st);
+
+int launch_combine(const float* pm, const float* pl, const float* po, int n_parts,
+                   int64_t ml_row, int64_t ml_part, int64_t o_row, int64_t o_part, void* out,
+                   int out_dtype, int64_t out_row, float* out_m, float* out_l, int n_rows,
+                   int head_dim, cudaStream_t st);
+
+}  // namespace knlp

@@ -1,0 +1,174 @@
+"""Generate the golden fixtures in this directory by running the REFERENCE's own
+kernels (mcgrof/knlp, fused-quant/fused_int4.v0.1.0.py) on CPU tensors under the
+Triton interpreter.
+
+Run once, where a checkout of the reference is available:
+
+    TRITON_INTERPRET=1 KNLP_REFERENCE=/path/to/knlp python tests/golden/make_golden.py
+
+The fixtures (.npz, a few hundred KB in total) are committed; tests read only
+them, never the reference checkout.  Inputs are stored as fp32 arrays holding
+values exactly representable in the named source dtype.
+"""
+
+import importlib.util
+import os
+import sys
+
+os.environ.setdefault("TRITON_INTERPRET", "1")
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REF = os.environ.get("KNLP_REFERENCE", "/root/reference")
+
+DT = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
+
+
+def load_reference():
+    path = os.path.join(REF, "fused-quant", "fused_int4.v0.1.0.py")
+    spec = importlib.util.spec_from_file_location("knlp_ref_fused_int4", path)
+    m = importlib.util.module_from_spec(spec)
+    sys.modules["knlp_ref_fused_int4"] = m
+    spec.loader.exec_module(m)
+    return m
+
+
+def make_kv(g, n, h, d, dtype, outlier=True, special_rows=True):
+    k = torch.randn(n, h, d, generator=g)
+    v = torch.randn(n, h, d, generator=g) + 0.3
+    if outlier:
+        k[:, :, 5] *= 10.0
+        v[:, :, d - 3] *= 10.0
+    if special_rows and n >= 6:
+        # all-zero row, constant row, exact .5 ties (range 15 -> scale 1),
+        # tiny range, symmetric ties (amax 7 -> scale 1)
+        k[0] = 0.0
+        v[0] = 0.0
+        k[1] = 1.25
+        v[1] = -3.0
+        ramp = torch.arange(32, dtype=torch.float32) * 0.5
+        ramp[-1] = 15.0
+        k[2, :, :32] = ramp
+        v[2, :, :32] = ramp - 4.0
+        k[3] = k[3] * 1e-6
+        v[3] = v[3] * 1e-9
+        sym = (torch.arange(32, dtype=torch.float32) - 16.0) * 0.5
+        sym[0] = -7.0
+        sym[-1] = 7.0
+        k[4, :, :32] = sym
+        v[4, :, :32] = sym
+        k[5, :, :32] = 0.0
+        k[5, :, 7] = 400.0  # one extreme outlier in an otherwise zero group
+        v[5, :, :32] = torch.linspace(-1, 1, 32)
+        v[5, :, 9] = -400.0
+    return k.to(dtype), v.to(dtype)
+
+
+def alloc_cache(nb, P, h, d, int8_k=False):
+    ng = d // 32
+    kc = torch.zeros(nb, P, h, d if int8_k else d // 2, dtype=torch.int8 if int8_k else torch.uint8)
+    vc = torch.zeros(nb, P, h, d // 2, dtype=torch.uint8)
+    mk = lambda: torch.zeros(nb, P, h, ng, dtype=torch.float16)
+    return kc, vc, mk(), mk(), mk(), mk()
+
+
+def f16_bits(t):
+    return t.view(torch.int16).numpy().view(np.uint16).copy()
+
+
+def gen_write_cases(m, out):
+    P = 16
+    for name, dtype, d, h, n in (("f32_d64", "f32", 64, 3, 24), ("bf16_d128", "bf16", 128, 2, 20),
+                                 ("f16_d128", "f16", 128, 2, 12)):
+        g = torch.Generator().manual_seed(1000 + d + n)
+        k, v = make_kv(g, n, h, d, DT[dtype])
+        nb = 4
+        perm = torch.randperm(nb * P, generator=g)[:n].to(torch.int64)
+        slots = perm.clone()
+        slots[n // 2] = -1
+        rec = dict(key=k.float().numpy(), value=v.float().numpy(), slot_mapping=slots.numpy(),
+                   src_dtype=dtype, block_size=P, num_blocks=nb)
+        # asymmetric K+V
+        kc, vc, ks, vs, kz, vz = alloc_cache(nb, P, h, d)
+        m.reshape_and_cache_int4(k, v, kc, vc, ks, vs, slots, kz, vz, asymmetric=True)
+        rec.update(asym_kc=kc.numpy().copy(), asym_vc=vc.numpy().copy(), asym_ks=f16_bits(ks),
+                   asym_vs=f16_bits(vs), asym_kz=f16_bits(kz), asym_vz=f16_bits(vz))
+        # symmetric K+V with the default outlier clip
+        kc, vc, ks, vs, _, _ = alloc_cache(nb, P, h, d)
+        m.reshape_and_cache_int4(k, v, kc, vc, ks, vs, slots, asymmetric=False)
+        rec.update(sym_kc=kc.numpy().copy(), sym_vc=vc.numpy().copy(), sym_ks=f16_bits(ks),
+                   sym_vs=f16_bits(vs), clip_ratio=float(m.OUTLIER_CLIP_RATIO))
+        # V only, asymmetric
+        _, vc, _, vs, _, vz = alloc_cache(nb, P, h, d)
+        m.reshape_and_cache_v_only_int4(v, vc, vs, slots, vz, asymmetric=True)
+        rec.update(vonly_vc=vc.numpy().copy(), vonly_vs=f16_bits(vs), vonly_vz=f16_bits(vz))
+        # K int8 group-32
+        kc8, _, ks, _, _, _ = alloc_cache(nb, P, h, d, int8_k=True)
+        m.reshape_and_cache_k_int8(k, kc8, ks, slots)
+        rec.update(int8_kc=kc8.numpy().copy(), int8_ks=f16_bits(ks))
+        out[f"write_{name}"] = rec
+        print("write", name, "done", flush=True)
+
+
+def gen_decode_cases(m, out):
+    P = 16
+    cases = (
+        # name, q dtype, Hq, Hkv, d, seq lens
+        ("mha_f32_d64", "f32", 3, 3, 64, (100, 37)),
+        ("gqa4_bf16_d128", "bf16", 8, 2, 128, (37, 16, 130)),
+        ("gqa8_f16_d128", "f16", 8, 1, 128, (65, 1)),
+    )
+    for name, dtype, hq, hkv, d, lens in cases:
+        g = torch.Generator().manual_seed(2000 + hq * 7 + d)
+        S = len(lens)
+        max_blocks = max((L + P - 1) // P for L in lens)
+        nb = S * max_blocks + 3
+        perm = torch.randperm(nb, generator=g)
+        bt = torch.zeros(S, max_blocks, dtype=torch.int32)
+        slots, toks = [], 0
+        for s, L in enumerate(lens):
+            bt[s] = perm[s * max_blocks:(s + 1) * max_blocks].to(torch.int32)
+            for n in range(L):
+                slots.append(int(bt[s, n // P]) * P + n % P)
+            toks += L
+        slots = torch.tensor(slots, dtype=torch.int64)
+        kvdt = DT[dtype]
+        k, v = make_kv(g, toks, hkv, d, kvdt, special_rows=False)
+        q = torch.randn(S, hq, d, generator=g).to(kvdt)
+        seq_lens = torch.tensor(lens, dtype=torch.int32)
+        rec = dict(query=q.float().numpy(), key=k.float().numpy(), value=v.float().numpy(),
+                   slot_mapping=slots.numpy(), block_table=bt.numpy(), seq_lens=seq_lens.numpy(),
+                   q_dtype=dtype, block_size=P, num_blocks=nb, num_kv_heads=hkv, head_size=d)
+        for mode, asym in (("asym", True), ("sym", False)):
+            kc, vc, ks, vs, kz, vz = alloc_cache(nb, P, hkv, d)
+            m.reshape_and_cache_int4(k, v, kc, vc, ks, vs, slots, kz if asym else None,
+                                     vz if asym else None, asymmetric=asym)
+            o = m.fused_int4_decode(q, kc, vc, ks, vs, bt, seq_lens, hkv, d, block_n=64,
+                                    k_zeros=kz if asym else None, v_zeros=vz if asym else None,
+                                    asymmetric=asym)
+            rec[f"{mode}_out"] = o.float().numpy()
+            rec[f"{mode}_out_dtype"] = str(o.dtype)
+        kc8, vc, ks, vs, _, vz = alloc_cache(nb, P, hkv, d, int8_k=True)
+        m.reshape_and_cache_k_int8(k, kc8, ks, slots)
+        m.reshape_and_cache_v_only_int4(v, vc, vs, slots, vz, asymmetric=True)
+        o = m.kint8_vint4_decode(q, kc8, vc, ks, vs, bt, seq_lens, hkv, d, block_n=64,
+                                 v_zeros=vz, asymmetric=True)
+        rec["k8v4_out"] = o.float().numpy()
+        out[f"decode_{name}"] = rec
+        print("decode", name, "done", flush=True)
+
+
+def main():
+    m = load_reference()
+    out = {}
+    gen_write_cases(m, out)
+    gen_decode_cases(m, out)
+    for name, rec in out.items():
+        np.savez_compressed(os.path.join(HERE, name + ".npz"), **rec)
+        print("saved", name)
+
+
+if __name__ == "__main__":
+    main()
