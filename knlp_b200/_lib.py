@@ -1,0 +1,95 @@
+"""ctypes binding of libknlp_b200.so (the C ABI declared in include/knlp_b200.h).
+
+There is no fallback: if the library is missing or does not export a symbol, the
+import of the operators fails with an error that says how to build it.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libknlp_b200.so")
+
+ABI_VERSION = 1
+
+# dtype / mode codes of include/knlp_b200.h
+F32, F16, BF16 = 0, 1, 2
+KV_NONE, KV_INT4_SYM, KV_INT4_ASYM, KV_INT8_G32 = 0, 1, 2, 3
+DECODE_FORCE_GENERIC = 1
+
+SYMBOLS = (
+    "knlp_b200_abi_version",
+    "knlp_b200_strerror",
+    "knlp_b200_quant_append",
+    "knlp_b200_decode_plan",
+    "knlp_b200_decode_splitk",
+    "knlp_b200_combine",
+)
+
+
+class KvPlane(C.Structure):
+    """knlp_kv_plane"""
+
+    _fields_ = [
+        ("codes", C.c_void_p),
+        ("scales", C.c_void_p),
+        ("zeros", C.c_void_p),
+        ("codes_stride", C.c_int64 * 3),
+        ("scales_stride", C.c_int64 * 3),
+        ("zeros_stride", C.c_int64 * 3),
+        ("mode", C.c_int32),
+        ("reserved", C.c_int32),
+    ]
+
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build the CUDA library first with "
+            "`python -m knlp_b200.build` (needs nvcc; no GPU needed to build). "
+            "knlp_b200 has no CPU or PyTorch fallback.")
+    lib = C.CDLL(LIB_PATH)
+    for s in SYMBOLS:
+        if not hasattr(lib, s):
+            raise RuntimeError(f"{LIB_PATH} does not export {s}; rebuild it")
+    I64P = C.POINTER(C.c_int64)
+    PL = C.POINTER(KvPlane)
+    lib.knlp_b200_abi_version.restype = C.c_int
+    lib.knlp_b200_abi_version.argtypes = []
+    lib.knlp_b200_strerror.restype = C.c_char_p
+    lib.knlp_b200_strerror.argtypes = [C.c_int]
+    lib.knlp_b200_quant_append.restype = C.c_int
+    lib.knlp_b200_quant_append.argtypes = [
+        C.c_void_p, I64P, C.c_void_p, I64P, C.c_int, PL, PL, C.c_void_p,
+        C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_void_p]
+    lib.knlp_b200_decode_plan.restype = C.c_int
+    lib.knlp_b200_decode_plan.argtypes = [
+        C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+        C.POINTER(C.c_int), C.POINTER(C.c_int64)]
+    lib.knlp_b200_decode_splitk.restype = C.c_int
+    lib.knlp_b200_decode_splitk.argtypes = [
+        C.c_void_p, C.c_int, I64P, PL, PL, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
+        C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+        C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint, C.c_void_p]
+    lib.knlp_b200_combine.restype = C.c_int
+    lib.knlp_b200_combine.argtypes = [
+        C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
+        C.c_void_p, C.c_int, C.c_int64, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+    if lib.knlp_b200_abi_version() != ABI_VERSION:
+        raise RuntimeError("libknlp_b200.so ABI version mismatch; rebuild it")
+    _lib = lib
+    return lib
+
+
+def check(status: int, what: str) -> None:
+    if status != 0:
+        msg = load().knlp_b200_strerror(status).decode()
+        raise RuntimeError(f"{what} failed: {msg} (status {status})")

@@ -1,0 +1,204 @@
+// C ABI of the library: argument validation and dispatch.  No exceptions, no
+// C++ types and no allocation cross this boundary.
+
+#include <mutex>
+
+#include "common.cuh"
+
+using namespace knlp;
+
+namespace {
+
+bool dtype_ok(int dt) { return dt == KNLP_F32 || dt == KNLP_F16 || dt == KNLP_BF16; }
+
+bool head_dim_ok(int d) { return d == 32 || d == 64 || d == 128 || d == 256; }
+
+int check_plane(const knlp_kv_plane* p, bool is_k) {
+  if (!p) return KNLP_ERR_NULL;
+  switch (p->mode) {
+    case KNLP_KV_INT4_SYM:
+      break;
+    case KNLP_KV_INT4_ASYM:
+      if (!p->zeros) return KNLP_ERR_NULL;
+      break;
+    case KNLP_KV_INT8_G32:
+      if (!is_k) return KNLP_ERR_MODE;  // int8 V is not built
+      break;
+    default:
+      return KNLP_ERR_MODE;
+  }
+  if (!p->codes || !p->scales) return KNLP_ERR_NULL;
+  return KNLP_OK;
+}
+
+int sm_count() {
+  static int cached = 0;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess &&
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) {
+      cached = n;
+    } else {
+      cudaGetLastError();
+      cached = 148;  // B200
+    }
+  });
+  return cached;
+}
+
+}  // namespace
+
+extern "C" {
+
+int knlp_b200_abi_version(void) { return KNLP_B200_ABI_VERSION; }
+
+const char* knlp_b200_strerror(int status) {
+  switch (status) {
+    case KNLP_OK: return "ok";
+    case KNLP_ERR_NULL: return "a required pointer is NULL";
+    case KNLP_ERR_SHAPE: return "unsupported shape (head_dim must be 32/64/128/256, heads must divide)";
+    case KNLP_ERR_DTYPE: return "unknown dtype code";
+    case KNLP_ERR_MODE: return "unknown or unsupported K/V quantization mode";
+    case KNLP_ERR_STRIDE: return "stride or alignment not addressable";
+    case KNLP_ERR_WORKSPACE: return "split count / workspace arguments out of range";
+    case KNLP_ERR_LAUNCH: return "CUDA launch failed";
+    case KNLP_ERR_NO_DEVICE: return "no usable sm_100 device or kernel image";
+    case KNLP_ERR_TOO_LARGE: return "request exceeds a fixed capacity of this entry point";
+    default: return "unknown status";
+  }
+}
+
+int knlp_b200_quant_append(const void* key, const int64_t key_stride[2], const void* value,
+                           const int64_t value_stride[2], int src_dtype,
+                           const knlp_kv_plane* k_plane, const knlp_kv_plane* v_plane,
+                           const int64_t* slot_mapping, int n_tokens, int n_kv_heads,
+                           int head_dim, int block_size, float clip_ratio, void* stream) {
+  if (!dtype_ok(src_dtype)) return KNLP_ERR_DTYPE;
+  if (n_tokens < 0 || n_kv_heads <= 0 || block_size <= 0) return KNLP_ERR_SHAPE;
+  if (head_dim <= 0 || head_dim % KNLP_GROUP_SIZE) return KNLP_ERR_SHAPE;
+  const bool do_k = key && k_plane && k_plane->mode != KNLP_KV_NONE;
+  const bool do_v = value && v_plane && v_plane->mode != KNLP_KV_NONE;
+  if (do_k) {
+    if (!key_stride) return KNLP_ERR_NULL;
+    int rc = check_plane(k_plane, true);
+    if (rc) return rc;
+  }
+  if (do_v) {
+    if (!value_stride) return KNLP_ERR_NULL;
+    int rc = check_plane(v_plane, false);
+    if (rc) return rc;
+  }
+  if (!do_k && !do_v) return KNLP_OK;
+  if (n_tokens == 0) return KNLP_OK;
+  if (!slot_mapping) return KNLP_ERR_NULL;
+  Plane kp = make_plane(do_k ? k_plane : nullptr);
+  Plane vp = make_plane(do_v ? v_plane : nullptr);
+  return launch_quant_append(do_k ? key : nullptr, key_stride, do_v ? value : nullptr,
+                             value_stride, src_dtype, kp, vp, slot_mapping, n_tokens, n_kv_heads,
+                             head_dim, block_size, clip_ratio, static_cast<cudaStream_t>(stream));
+}
+
+int knlp_b200_decode_plan(int n_seqs, int n_q_heads, int n_kv_heads, int head_dim,
+                          int block_size, int max_seq_len, int k_mode, int v_mode,
+                          int* n_splits_out, int64_t* workspace_floats_out) {
+  (void)block_size; (void)k_mode; (void)v_mode;
+  if (!n_splits_out || !workspace_floats_out) return KNLP_ERR_NULL;
+  if (n_seqs <= 0 || n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads)
+    return KNLP_ERR_SHAPE;
+  if (!head_dim_ok(head_dim) || max_seq_len < 0) return KNLP_ERR_SHAPE;
+  // CTAs per split: one per (sequence, block of up to 8 kv heads).  Two CTAs fit on
+  // an SM.  Pick the split count that fills whole waves best; prefer at least two
+  // waves so the tail is amortised, and never go below 256 tokens per split.
+  int hpb = 8;
+  while (hpb > 1 && n_kv_heads % hpb) hpb >>= 1;
+  const int64_t base = static_cast<int64_t>(n_seqs) * (n_kv_heads / hpb);
+  const int64_t slots = 2LL * sm_count();
+  const int max_splits = max_seq_len >= 512 ? (max_seq_len / 256 > 1024 ? 1024 : max_seq_len / 256) : 1;
+  int best = 1;
+  double best_score = -1.0;
+  for (int n = 1; n <= max_splits; ++n) {
+    const int64_t ctas = base * n;
+    const int64_t waves = (ctas + slots - 1) / slots;
+    if (waves > 6 && n > 1) break;
+    const double eff = static_cast<double>(ctas) / static_cast<double>(waves * slots);
+    // more waves smooth out uneven sequence lengths; weight them mildly
+    const double score = eff * (1.0 - 0.08 / static_cast<double>(waves));
+    if (score > best_score + 1e-9) {
+      best_score = score;
+      best = n;
+    }
+  }
+  *n_splits_out = best;
+  *workspace_floats_out =
+      static_cast<int64_t>(n_seqs) * n_q_heads * best * (static_cast<int64_t>(head_dim) + 2);
+  return KNLP_OK;
+}
+
+int knlp_b200_decode_splitk(const void* query, int q_dtype, const int64_t q_stride[2],
+                            const knlp_kv_plane* k_plane, const knlp_kv_plane* v_plane,
+                            const int32_t* block_table, int64_t bt_stride,
+                            const int32_t* seq_lens, int64_t num_blocks, int n_seqs,
+                            int n_q_heads, int n_kv_heads, int head_dim, int block_size,
+                            int n_splits, int max_seq_len, float* part_m, float* part_l,
+                            float* part_o, unsigned flags, void* stream) {
+  if (!query || !q_stride || !block_table || !seq_lens || !part_m || !part_l || !part_o)
+    return KNLP_ERR_NULL;
+  if (!dtype_ok(q_dtype)) return KNLP_ERR_DTYPE;
+  if (n_seqs < 0 || n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads)
+    return KNLP_ERR_SHAPE;
+  if (!head_dim_ok(head_dim) || block_size <= 0 || num_blocks <= 0) return KNLP_ERR_SHAPE;
+  if (n_seqs > 65535 || n_kv_heads * ((n_q_heads / n_kv_heads + 7) / 8) > 65535)
+    return KNLP_ERR_SHAPE;
+  if (n_splits < 1 || max_seq_len < 0) return KNLP_ERR_WORKSPACE;
+  int rc = check_plane(k_plane, true);
+  if (rc) return rc;
+  rc = check_plane(v_plane, false);
+  if (rc) return rc;
+  if (n_seqs == 0) return KNLP_OK;
+
+  DecodeArgs a{};
+  a.q = query;
+  a.q_dtype = q_dtype;
+  a.q_stride[0] = q_stride[0];
+  a.q_stride[1] = q_stride[1];
+  a.k = make_plane(k_plane);
+  a.v = make_plane(v_plane);
+  a.block_table = block_table;
+  a.bt_stride = bt_stride;
+  a.seq_lens = seq_lens;
+  a.num_blocks = num_blocks;
+  a.n_seqs = n_seqs;
+  a.n_q_heads = n_q_heads;
+  a.n_kv_heads = n_kv_heads;
+  a.head_dim = head_dim;
+  a.block_size = block_size;
+  a.n_splits = n_splits;
+  a.chunk = split_chunk(max_seq_len, n_splits);
+  a.part_m = part_m;
+  a.part_l = part_l;
+  a.part_o = part_o;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (!(flags & KNLP_DECODE_FORCE_GENERIC)) {
+    rc = launch_decode_mma(a, st);
+    if (rc <= 0) return rc;  // launched, or failed for good
+  }
+  return launch_decode_generic(a, st);
+}
+
+int knlp_b200_combine(const float* part_m, const float* part_l, const float* part_o,
+                      int n_parts, int64_t ml_row_stride, int64_t ml_part_stride,
+                      int64_t o_row_stride, int64_t o_part_stride, void* out, int out_dtype,
+                      int64_t out_row_stride, float* out_m, float* out_l, int n_rows,
+                      int head_dim, void* stream) {
+  if (!part_m || !part_l || !part_o || !out) return KNLP_ERR_NULL;
+  if ((out_m == nullptr) != (out_l == nullptr)) return KNLP_ERR_NULL;
+  if (!dtype_ok(out_dtype)) return KNLP_ERR_DTYPE;
+  if (out_m && out_dtype != KNLP_F32) return KNLP_ERR_DTYPE;
+  if (n_parts < 1 || n_rows < 0 || head_dim <= 0) return KNLP_ERR_SHAPE;
+  return launch_combine(part_m, part_l, part_o, n_parts, ml_row_stride, ml_part_stride,
+                        o_row_stride, o_part_stride, out, out_dtype, out_row_stride, out_m,
+                        out_l, n_rows, head_dim, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

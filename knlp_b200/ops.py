@@ -1,0 +1,356 @@
+"""Operator surface of the packed-KV hot path, with the reference's signatures.
+
+Drop-in for the module-level functions of mcgrof/knlp's
+``fused-quant/fused_int4.v0.1.0.py``:
+
+    reshape_and_cache_int4          (:418-472)
+    reshape_and_cache_v_only_int4   (:603-647)
+    reshape_and_cache_k_int8        (:1287-1312)
+    fused_int4_decode               (:901-979)
+    kint8_vint4_decode              (:1496-1554)
+
+Same argument names, order, meaning and in-place behaviour; tensors are CUDA
+tensors owned by the caller.  The work is done by hand-written sm_100a kernels in
+libknlp_b200.so, reached through its C ABI (include/knlp_b200.h) with raw device
+pointers; torch only supplies memory and the current stream.  There is no CPU or
+eager fallback: a CPU tensor, or a missing library, raises.
+
+Additions that the reference does not have (keyword-only, all optional):
+``out_dtype`` (fp32 output straight from the fp32 accumulator), ``max_seq_len``
+(host-known bound on ``seq_lens``; default ``block_table.shape[1] * block_size``,
+so that no device value is read back), ``n_splits``, ``force_generic``, and the
+split-context entry points ``decode_partials`` / ``combine_partials`` used by the
+multi-GPU context shard.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+# Environment defaults honoured like the reference (fused_int4.v0.1.0.py:55-78).
+GROUP_SIZE: int = int(os.environ.get("VLLM_FUSED_INT4_GROUP_SIZE", "32"))
+OUTLIER_CLIP_RATIO: float = float(os.environ.get("VLLM_FUSED_INT4_OUTLIER_CLIP_RATIO", "10.0"))
+ASYMMETRIC: bool = os.environ.get("VLLM_FUSED_INT4_ASYMMETRIC", "0") == "1"
+
+if GROUP_SIZE != 32:
+    raise RuntimeError("knlp_b200 is built for VLLM_FUSED_INT4_GROUP_SIZE=32 only")
+
+_DT = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise TypeError(f"unsupported dtype {t.dtype}; expected float32/float16/bfloat16") from None
+
+
+def _need_cuda(*tensors) -> torch.device:
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError("knlp_b200 operators take CUDA tensors only (no CPU fallback)")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise RuntimeError("all tensors must live on the same CUDA device")
+    return dev
+
+
+def _stride3(t: torch.Tensor):
+    if t.dim() != 4 or t.stride(3) != 1:
+        raise ValueError("cache tensors must be 4-D with a contiguous last dimension")
+    return (C.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
+
+
+def _stride2(t: torch.Tensor):
+    if t.dim() != 3 or t.stride(2) != 1:
+        raise ValueError("expected [n, heads, head_size] with a contiguous last dimension")
+    return (C.c_int64 * 2)(t.stride(0), t.stride(1))
+
+
+def _plane(codes, scales, zeros, mode) -> _lib.KvPlane:
+    p = _lib.KvPlane()
+    if codes.dtype not in (torch.uint8, torch.int8):
+        raise TypeError("code cache must be uint8 (INT4) or int8 (INT8)")
+    if scales.dtype != torch.float16 or (zeros is not None and zeros.dtype != torch.float16):
+        raise TypeError("scales and zeros must be float16")
+    p.codes = codes.data_ptr()
+    p.scales = scales.data_ptr()
+    p.zeros = zeros.data_ptr() if zeros is not None else None
+    p.codes_stride = _stride3(codes)
+    p.scales_stride = _stride3(scales)
+    p.zeros_stride = _stride3(zeros) if zeros is not None else (C.c_int64 * 3)(0, 0, 0)
+    p.mode = mode
+    return p
+
+
+def _int4_mode(asymmetric: bool, zeros) -> int:
+    if asymmetric:
+        if zeros is None:
+            raise ValueError("asymmetric=True needs the zero-point cache")
+        return _lib.KV_INT4_ASYM
+    return _lib.KV_INT4_SYM
+
+
+def _stream(dev) -> int:
+    return torch.cuda.current_stream(dev).cuda_stream
+
+
+def _quant_append(key, value, k_plane, v_plane, slot_mapping, head_size, block_size, clip_ratio):
+    src = key if key is not None else value
+    dev = _need_cuda(key, value, slot_mapping)
+    if slot_mapping.dtype != torch.int64 or slot_mapping.dim() != 1 or (
+            slot_mapping.numel() and slot_mapping.stride(0) != 1):
+        raise TypeError("slot_mapping must be a contiguous int64 vector")
+    if key is not None and value is not None and key.dtype != value.dtype:
+        raise TypeError("key and value must have the same dtype")
+    n_tokens, n_heads = src.shape[0], src.shape[1]
+    if slot_mapping.numel() != n_tokens:
+        raise ValueError("slot_mapping length must equal the number of tokens")
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        rc = lib.knlp_b200_quant_append(
+            key.data_ptr() if key is not None else None,
+            _stride2(key) if key is not None else None,
+            value.data_ptr() if value is not None else None,
+            _stride2(value) if value is not None else None,
+            _dt(src),
+            C.byref(k_plane) if k_plane is not None else None,
+            C.byref(v_plane) if v_plane is not None else None,
+            slot_mapping.data_ptr(), n_tokens, n_heads, head_size, block_size,
+            float(clip_ratio), _stream(dev))
+    _lib.check(rc, "knlp_b200_quant_append")
+
+
+def reshape_and_cache_int4(
+    key: torch.Tensor,  # [num_tokens, num_heads, head_size]
+    value: torch.Tensor,
+    key_cache: torch.Tensor,  # [num_blocks, block_size, num_heads, head_size//2] uint8
+    value_cache: torch.Tensor,
+    k_scales: torch.Tensor,  # [num_blocks, block_size, num_heads, head_size//32] fp16
+    v_scales: torch.Tensor,
+    slot_mapping: torch.Tensor,  # [num_tokens] int64, <0 = skip
+    k_zeros: Optional[torch.Tensor] = None,
+    v_zeros: Optional[torch.Tensor] = None,
+    asymmetric: bool = False,
+    *,
+    clip_ratio: Optional[float] = None,
+) -> None:
+    """Quantize K/V to INT4 and write them into the paged cache, in place
+    (reference fused_int4.v0.1.0.py:418-472).  Packed bytes, scales and zeros are
+    bit-identical to the reference kernel's."""
+    _need_cuda(key_cache, value_cache, k_scales, v_scales, k_zeros, v_zeros)
+    head_size = key.shape[2]
+    kp = _plane(key_cache, k_scales, k_zeros if asymmetric else None,
+                _int4_mode(asymmetric, k_zeros))
+    vp = _plane(value_cache, v_scales, v_zeros if asymmetric else None,
+                _int4_mode(asymmetric, v_zeros))
+    _quant_append(key, value, kp, vp, slot_mapping, head_size, key_cache.shape[1],
+                  OUTLIER_CLIP_RATIO if clip_ratio is None else clip_ratio)
+
+
+def reshape_and_cache_v_only_int4(
+    value: torch.Tensor,
+    value_cache: torch.Tensor,
+    v_scales: torch.Tensor,
+    slot_mapping: torch.Tensor,
+    v_zeros: Optional[torch.Tensor] = None,
+    asymmetric: bool = False,
+    *,
+    clip_ratio: Optional[float] = None,
+) -> None:
+    """V-only variant (reference fused_int4.v0.1.0.py:603-647)."""
+    _need_cuda(value_cache, v_scales, v_zeros)
+    vp = _plane(value_cache, v_scales, v_zeros if asymmetric else None,
+                _int4_mode(asymmetric, v_zeros))
+    _quant_append(None, value, None, vp, slot_mapping, value.shape[2], value_cache.shape[1],
+                  OUTLIER_CLIP_RATIO if clip_ratio is None else clip_ratio)
+
+
+def reshape_and_cache_k_int8(
+    key: torch.Tensor,
+    key_cache_int8: torch.Tensor,  # [num_blocks, block_size, num_heads, head_size] int8
+    k_scales: torch.Tensor,
+    slot_mapping: torch.Tensor,
+) -> None:
+    """K -> symmetric INT8 with per-group-32 fp16 scales (reference :1287-1312)."""
+    _need_cuda(key_cache_int8, k_scales)
+    kp = _plane(key_cache_int8, k_scales, None, _lib.KV_INT8_G32)
+    _quant_append(key, None, kp, None, slot_mapping, key.shape[2], key_cache_int8.shape[1], 0.0)
+
+
+def plan_splits(num_seqs: int, num_heads: int, num_kv_heads: int, head_size: int,
+                block_size: int, max_seq_len: int) -> int:
+    """Split count the library recommends for this decode shape (host arithmetic)."""
+    n = C.c_int(0)
+    ws = C.c_int64(0)
+    rc = _lib.load().knlp_b200_decode_plan(num_seqs, num_heads, num_kv_heads, head_size,
+                                           block_size, max_seq_len, 0, 0, C.byref(n), C.byref(ws))
+    _lib.check(rc, "knlp_b200_decode_plan")
+    return n.value
+
+
+def decode_partials(
+    query: torch.Tensor, k_plane: _lib.KvPlane, v_plane: _lib.KvPlane, num_blocks: int,
+    block_table: torch.Tensor, seq_lens: torch.Tensor, num_kv_heads: int, head_size: int,
+    block_size: int, *, max_seq_len: Optional[int] = None, n_splits: Optional[int] = None,
+    force_generic: bool = False,
+) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Run the split-context decode kernel and return the softmax partials
+    (m [S, Hq, n], l [S, Hq, n], o [S, Hq, n, d]) — m in the natural-log domain,
+    o un-normalised."""
+    dev = _need_cuda(query, block_table, seq_lens)
+    if block_table.dtype != torch.int32 or seq_lens.dtype != torch.int32:
+        raise TypeError("block_table and seq_lens must be int32")
+    if block_table.dim() != 2 or block_table.stride(1) != 1 or seq_lens.dim() != 1 or (
+            seq_lens.numel() and seq_lens.stride(0) != 1):
+        raise ValueError("block_table must be [S, max_blocks] (contiguous rows), seq_lens [S]")
+    S, Hq, d = query.shape
+    if d != head_size or Hq % num_kv_heads:
+        raise ValueError("query shape does not match num_kv_heads / head_size")
+    if max_seq_len is None:
+        max_seq_len = block_table.shape[1] * block_size
+    if n_splits is None:
+        n_splits = plan_splits(S, Hq, num_kv_heads, head_size, block_size, max_seq_len)
+    pm = torch.empty((S, Hq, n_splits), dtype=torch.float32, device=dev)
+    pl = torch.empty((S, Hq, n_splits), dtype=torch.float32, device=dev)
+    po = torch.empty((S, Hq, n_splits, d), dtype=torch.float32, device=dev)
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        rc = lib.knlp_b200_decode_splitk(
+            query.data_ptr(), _dt(query), _stride2(query), C.byref(k_plane), C.byref(v_plane),
+            block_table.data_ptr(), block_table.stride(0), seq_lens.data_ptr(), num_blocks,
+            S, Hq, num_kv_heads, head_size, block_size, n_splits, max_seq_len,
+            pm.data_ptr(), pl.data_ptr(), po.data_ptr(),
+            _lib.DECODE_FORCE_GENERIC if force_generic else 0, _stream(dev))
+    _lib.check(rc, "knlp_b200_decode_splitk")
+    return pm, pl, po
+
+
+def combine_partials(pm: torch.Tensor, pl: torch.Tensor, po: torch.Tensor,
+                     out: Optional[torch.Tensor] = None, out_dtype=torch.float32,
+                     emit_partial: bool = False, parts_dim: int = -1):
+    """Merge softmax partials.
+
+    pm, pl: [..., n_parts] and po: [..., n_parts, d] (``parts_dim=-1``), or with the
+    parts dimension first, pm, pl: [n_parts, ...], po: [n_parts, ..., d]
+    (``parts_dim=0``, the layout an all-gather of per-rank partials produces).
+    Returns the normalised output [..., d] in ``out_dtype``; with
+    ``emit_partial=True`` returns the merged partial (m [...], l [...], o [..., d])
+    in fp32 instead.
+    """
+    dev = _need_cuda(pm, pl, po)
+    if not (pm.is_contiguous() and pl.is_contiguous() and po.is_contiguous()):
+        raise ValueError("partials must be contiguous")
+    d = po.shape[-1]
+    if parts_dim == 0:
+        n_parts = pm.shape[0]
+        rows_shape = tuple(pm.shape[1:])
+        n_rows = pm[0].numel()
+        ml_row, ml_part, o_row, o_part = 1, n_rows, d, n_rows * d
+    else:
+        n_parts = pm.shape[-1]
+        rows_shape = tuple(pm.shape[:-1])
+        n_rows = pm.numel() // max(n_parts, 1)
+        ml_row, ml_part, o_row, o_part = n_parts, 1, n_parts * d, d
+    lib = _lib.load()
+    if emit_partial:
+        om = torch.empty(rows_shape, dtype=torch.float32, device=dev)
+        ol = torch.empty(rows_shape, dtype=torch.float32, device=dev)
+        oo = torch.empty(rows_shape + (d,), dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            rc = lib.knlp_b200_combine(pm.data_ptr(), pl.data_ptr(), po.data_ptr(), n_parts,
+                                       ml_row, ml_part, o_row, o_part, oo.data_ptr(), _lib.F32, d,
+                                       om.data_ptr(), ol.data_ptr(), n_rows, d, _stream(dev))
+        _lib.check(rc, "knlp_b200_combine")
+        return om, ol, oo
+    if out is None:
+        out = torch.empty(rows_shape + (d,), dtype=out_dtype, device=dev)
+    elif not out.is_contiguous() or out.numel() != n_rows * d:
+        raise ValueError("out must be contiguous [..., d]")
+    with torch.cuda.device(dev):
+        rc = lib.knlp_b200_combine(pm.data_ptr(), pl.data_ptr(), po.data_ptr(), n_parts,
+                                   ml_row, ml_part, o_row, o_part, out.data_ptr(), _DT[out.dtype],
+                                   d, None, None, n_rows, d, _stream(dev))
+    _lib.check(rc, "knlp_b200_combine")
+    return out
+
+
+def _decode(query, k_plane, v_plane, num_blocks, block_table, seq_lens, num_kv_heads,
+            head_size, block_size, out_dtype, max_seq_len, n_splits, force_generic):
+    pm, pl, po = decode_partials(query, k_plane, v_plane, num_blocks, block_table, seq_lens,
+                                 num_kv_heads, head_size, block_size, max_seq_len=max_seq_len,
+                                 n_splits=n_splits, force_generic=force_generic)
+    return combine_partials(pm, pl, po, out_dtype=query.dtype if out_dtype is None else out_dtype)
+
+
+def fused_int4_decode(
+    query: torch.Tensor,  # [num_seqs, num_heads, head_size]
+    key_cache: torch.Tensor,  # [num_blocks, block_size, num_kv_heads, head_size//2]
+    value_cache: torch.Tensor,
+    k_scales: torch.Tensor,  # [num_blocks, block_size, num_kv_heads, head_size//32]
+    v_scales: torch.Tensor,
+    block_table: torch.Tensor,  # [num_seqs, max_num_blocks_per_seq] int32
+    seq_lens: torch.Tensor,  # [num_seqs] int32
+    num_kv_heads: int,
+    head_size: int,
+    block_n: int = 64,  # tuning hint of the reference kernel; ignored here
+    k_zeros: Optional[torch.Tensor] = None,
+    v_zeros: Optional[torch.Tensor] = None,
+    asymmetric: bool = False,
+    *,
+    out_dtype: Optional[torch.dtype] = None,
+    max_seq_len: Optional[int] = None,
+    n_splits: Optional[int] = None,
+    force_generic: bool = False,
+) -> torch.Tensor:
+    """Decode attention over the packed INT4 cache (reference :901-979).
+
+    Returns [num_seqs, num_heads, head_size] in the query dtype (``out_dtype``
+    overrides; fp32 is the un-rounded accumulator).  Sequences of length 0 give 0.
+    """
+    _need_cuda(key_cache, value_cache, k_scales, v_scales, k_zeros, v_zeros)
+    kp = _plane(key_cache, k_scales, k_zeros if asymmetric else None,
+                _int4_mode(asymmetric, k_zeros))
+    vp = _plane(value_cache, v_scales, v_zeros if asymmetric else None,
+                _int4_mode(asymmetric, v_zeros))
+    return _decode(query, kp, vp, key_cache.shape[0], block_table, seq_lens, num_kv_heads,
+                   head_size, key_cache.shape[1], out_dtype, max_seq_len, n_splits, force_generic)
+
+
+def kint8_vint4_decode(
+    query: torch.Tensor,
+    key_cache_int8: torch.Tensor,  # [num_blocks, block_size, kv_heads, head_size] int8
+    value_cache_int4: torch.Tensor,  # [num_blocks, block_size, kv_heads, head_size//2] uint8
+    k_scales: torch.Tensor,
+    v_scales: torch.Tensor,
+    block_table: torch.Tensor,
+    seq_lens: torch.Tensor,
+    num_kv_heads: int,
+    head_size: int,
+    block_n: int = 64,
+    v_zeros: Optional[torch.Tensor] = None,
+    asymmetric: bool = False,
+    *,
+    out_dtype: Optional[torch.dtype] = None,
+    max_seq_len: Optional[int] = None,
+    n_splits: Optional[int] = None,
+    force_generic: bool = False,
+) -> torch.Tensor:
+    """K INT8 (group-32 scales) / V INT4 decode attention (reference :1496-1554)."""
+    _need_cuda(key_cache_int8, value_cache_int4, k_scales, v_scales, v_zeros)
+    kp = _plane(key_cache_int8, k_scales, None, _lib.KV_INT8_G32)
+    vp = _plane(value_cache_int4, v_scales, v_zeros if asymmetric else None,
+                _int4_mode(asymmetric, v_zeros))
+    return _decode(query, kp, vp, key_cache_int8.shape[0], block_table, seq_lens, num_kv_heads,
+                   head_size, key_cache_int8.shape[1], out_dtype, max_seq_len, n_splits,
+                   force_generic)

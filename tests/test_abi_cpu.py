@@ -1,0 +1,125 @@
+"""CPU checks of the C-ABI library: it loads, exports every function that
+include/knlp_b200.h declares, and rejects bad arguments on the host with the
+documented status codes (no kernel is launched in this file)."""
+
+import ctypes as C
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from knlp_b200 import _lib, build
+    build.build()
+    return _lib.load()
+
+
+def declared_functions():
+    text = open(os.path.join(ROOT, "include", "knlp_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(knlp_b200_\w+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported(lib):
+    from knlp_b200 import _lib
+    names = declared_functions()
+    assert names, "no declarations parsed"
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in the header but not exported"
+    assert set(names) == set(_lib.SYMBOLS), "python binding list and header disagree"
+
+
+def test_abi_version_and_strerror(lib):
+    assert lib.knlp_b200_abi_version() == 1
+    assert lib.knlp_b200_strerror(0) == b"ok"
+    for code in range(-9, 0):
+        assert len(lib.knlp_b200_strerror(code)) > 3
+
+
+def test_argument_errors_are_reported_on_the_host(lib):
+    from knlp_b200 import _lib
+    null = None
+    # NULL query
+    rc = lib.knlp_b200_decode_splitk(null, 0, null, null, null, null, 0, null, 1, 1, 4, 4, 64, 16,
+                                     1, 16, null, null, null, 0, null)
+    assert rc == -1
+    # bad dtype
+    st2 = (C.c_int64 * 2)(64, 64)
+    buf = C.create_string_buffer(64)
+    p = C.cast(buf, C.c_void_p)
+    rc = lib.knlp_b200_decode_splitk(p, 7, st2, null, null, p, 1, p, 1, 1, 4, 4, 64, 16, 1, 16,
+                                     p, p, p, 0, null)
+    assert rc == -3
+    # heads do not divide
+    rc = lib.knlp_b200_decode_splitk(p, 0, st2, null, null, p, 1, p, 1, 1, 5, 4, 64, 16, 1, 16,
+                                     p, p, p, 0, null)
+    assert rc == -2
+    # head_dim not supported
+    rc = lib.knlp_b200_decode_splitk(p, 0, st2, null, null, p, 1, p, 1, 1, 4, 4, 48, 16, 1, 16,
+                                     p, p, p, 0, null)
+    assert rc == -2
+    # missing plane
+    rc = lib.knlp_b200_decode_splitk(p, 0, st2, null, null, p, 1, p, 1, 1, 4, 4, 64, 16, 1, 16,
+                                     p, p, p, 0, null)
+    assert rc == -1
+    # asymmetric plane without zeros; int8 V
+    pl = _lib.KvPlane()
+    pl.codes = p.value
+    pl.scales = p.value
+    pl.mode = _lib.KV_INT4_ASYM
+    rc = lib.knlp_b200_decode_splitk(p, 0, st2, C.byref(pl), C.byref(pl), p, 1, p, 1, 1, 4, 4, 64,
+                                     16, 1, 16, p, p, p, 0, null)
+    assert rc == -1
+    pk = _lib.KvPlane(); pk.codes = p.value; pk.scales = p.value; pk.mode = _lib.KV_INT4_SYM
+    pv = _lib.KvPlane(); pv.codes = p.value; pv.scales = p.value; pv.mode = _lib.KV_INT8_G32
+    rc = lib.knlp_b200_decode_splitk(p, 0, st2, C.byref(pk), C.byref(pv), p, 1, p, 1, 1, 4, 4, 64,
+                                     16, 1, 16, p, p, p, 0, null)
+    assert rc == -4
+    # n_splits < 1
+    rc = lib.knlp_b200_decode_splitk(p, 0, st2, C.byref(pk), C.byref(pk), p, 1, p, 1, 1, 4, 4, 64,
+                                     16, 0, 16, p, p, p, 0, null)
+    assert rc == -6
+    # quant_append: bad dtype / odd head_dim; nothing to do is OK
+    assert lib.knlp_b200_quant_append(p, st2, p, st2, 9, C.byref(pk), C.byref(pk), p, 1, 1, 64, 16,
+                                      0.0, null) == -3
+    assert lib.knlp_b200_quant_append(p, st2, p, st2, 0, C.byref(pk), C.byref(pk), p, 1, 1, 40, 16,
+                                      0.0, null) == -2
+    assert lib.knlp_b200_quant_append(null, null, null, null, 0, null, null, null, 5, 1, 64, 16,
+                                      0.0, null) == 0
+    # combine
+    assert lib.knlp_b200_combine(null, null, null, 1, 1, 1, 1, 1, null, 0, 1, null, null, 1, 64,
+                                 null) == -1
+    assert lib.knlp_b200_combine(p, p, p, 0, 1, 1, 1, 1, p, 0, 1, null, null, 1, 64, null) == -2
+    assert lib.knlp_b200_combine(p, p, p, 1, 1, 1, 1, 1, p, 1, 1, p, p, 1, 64, null) == -3
+
+
+def test_decode_plan_fills_waves(lib):
+    n = C.c_int(0)
+    ws = C.c_int64(0)
+    # batch 32 x 128K, 8 kv heads: 32 CTAs per split, 296 slots on 148 SMs
+    assert lib.knlp_b200_decode_plan(32, 32, 8, 128, 16, 131072, 2, 2, C.byref(n), C.byref(ws)) == 0
+    assert n.value >= 9 and (32 * n.value) % 296 <= 296  # sane
+    waves = -(-32 * n.value // 296)
+    assert 32 * n.value / (waves * 296) > 0.9
+    assert ws.value == 32 * 32 * n.value * 130
+    # short context: one split
+    assert lib.knlp_b200_decode_plan(4, 8, 2, 128, 16, 100, 2, 2, C.byref(n), C.byref(ws)) == 0
+    assert n.value == 1
+    assert lib.knlp_b200_decode_plan(4, 9, 2, 128, 16, 100, 2, 2, C.byref(n), C.byref(ws)) == -2
+
+
+def test_ops_refuse_cpu_tensors_and_missing_library(monkeypatch):
+    import torch
+    from knlp_b200 import _lib, ops
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        ops.reshape_and_cache_k_int8(torch.zeros(1, 1, 32), torch.zeros(1, 16, 1, 32, dtype=torch.int8),
+                                     torch.zeros(1, 16, 1, 1, dtype=torch.float16),
+                                     torch.zeros(1, dtype=torch.int64))
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", "/nonexistent/libknlp_b200.so")
+    with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
+        _lib.load()
