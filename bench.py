@@ -236,7 +236,7 @@ def run_ours(args):
           for _ in range(K)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sampler = ClockSampler(local)
-    if rank == 0:
+    if rank == 0 and not args.profile:
         sampler.start()
         time.sleep(0.25)
     barrier()
@@ -248,11 +248,21 @@ def run_ours(args):
     total_ms = e0.elapsed_time(e1)
     kern_ms = sum(a.elapsed_time(b) for a, b in ev) / K
     # keep the sampler running for at least ~0.6 s of load so it sees the clocks
-    t_end = time.time() + 0.6
+    t_end = time.time() + (0.0 if args.profile else 0.6)
     while time.time() < t_end:
         step(w.seq_lens, w.max_seq_len)
     torch.cuda.synchronize()
     clocks = sampler.stop() if rank == 0 else None
+    if args.profile:
+        # profiling run (under ncu): kernel timing only, no end-to-end or CPU legs
+        if rank == 0:
+            print(json.dumps({"profile_run": True, "workload": args.workload,
+                              "ms_per_step": total_ms / K, "kernel_us": kern_ms * 1e3,
+                              "n_splits": n_splits, "algorithmic_bytes": w.algorithmic_bytes()}),
+                  flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     # ---------------- end to end through the operator API with host buffers
     L = w.seq_lens_host
@@ -354,6 +364,8 @@ def main():
     ap.add_argument("--scale", type=float, default=1.0)
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--profile", action="store_true",
+                    help="short run for use under ncu: timed steps only, one JSON line of timings")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

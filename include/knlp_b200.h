@@ -149,13 +149,15 @@ int knlp_b200_decode_splitk(const void* query, int q_dtype, const int64_t q_stri
  *   out          [n_rows, head_dim] with row stride out_row_stride (elements) of
  *                out_dtype: normalised attention output; rows with no tokens give 0
  *   out_m/out_l  if both non-NULL, the merged partial is emitted instead: out
- *                (must be KNLP_F32) receives the UN-normalised o, out_m/out_l [n_rows]
+ *                (must be KNLP_F32) receives the UN-normalised o, and row r's m and l
+ *                go to out_m[r*out_ml_stride], out_l[r*out_ml_stride] — so one buffer
+ *                of rows [o(head_dim), m, l] can be filled for a single all-gather
  */
 int knlp_b200_combine(const float* part_m, const float* part_l, const float* part_o,
                       int n_parts, int64_t ml_row_stride, int64_t ml_part_stride,
                       int64_t o_row_stride, int64_t o_part_stride,
                       void* out, int out_dtype, int64_t out_row_stride,
-                      float* out_m, float* out_l,
+                      float* out_m, float* out_l, int64_t out_ml_stride,
                       int n_rows, int head_dim, void* stream);
 
 #ifdef __cplusplus

@@ -82,7 +82,8 @@ def load() -> C.CDLL:
     lib.knlp_b200_combine.restype = C.c_int
     lib.knlp_b200_combine.argtypes = [
         C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
-        C.c_void_p, C.c_int, C.c_int64, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+        C.c_void_p, C.c_int, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int,
+        C.c_void_p]
     if lib.knlp_b200_abi_version() != ABI_VERSION:
         raise RuntimeError("libknlp_b200.so ABI version mismatch; rebuild it")
     _lib = lib

@@ -189,8 +189,8 @@ int knlp_b200_decode_splitk(const void* query, int q_dtype, const int64_t q_stri
 int knlp_b200_combine(const float* part_m, const float* part_l, const float* part_o,
                       int n_parts, int64_t ml_row_stride, int64_t ml_part_stride,
                       int64_t o_row_stride, int64_t o_part_stride, void* out, int out_dtype,
-                      int64_t out_row_stride, float* out_m, float* out_l, int n_rows,
-                      int head_dim, void* stream) {
+                      int64_t out_row_stride, float* out_m, float* out_l,
+                      int64_t out_ml_stride, int n_rows, int head_dim, void* stream) {
   if (!part_m || !part_l || !part_o || !out) return KNLP_ERR_NULL;
   if ((out_m == nullptr) != (out_l == nullptr)) return KNLP_ERR_NULL;
   if (!dtype_ok(out_dtype)) return KNLP_ERR_DTYPE;
@@ -198,7 +198,8 @@ int knlp_b200_combine(const float* part_m, const float* part_l, const float* par
   if (n_parts < 1 || n_rows < 0 || head_dim <= 0) return KNLP_ERR_SHAPE;
   return launch_combine(part_m, part_l, part_o, n_parts, ml_row_stride, ml_part_stride,
                         o_row_stride, o_part_stride, out, out_dtype, out_row_stride, out_m,
-                        out_l, n_rows, head_dim, static_cast<cudaStream_t>(stream));
+                        out_l, out_ml_stride, n_rows, head_dim,
+                        static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -18,7 +18,7 @@ __global__ void __launch_bounds__(kThreads)
 combine_kernel(const float* __restrict__ pm, const float* __restrict__ pl,
                const float* __restrict__ po, int n_parts, int64_t ml_row, int64_t ml_part,
                int64_t o_row, int64_t o_part, void* out, int out_dtype, int64_t out_row,
-               float* out_m, float* out_l, int head_dim) {
+               float* out_m, float* out_l, int64_t out_ml, int head_dim) {
   const int64_t row = blockIdx.x;
   const float* rm = pm + row * ml_row;
   const float* rl = pl + row * ml_row;
@@ -41,8 +41,8 @@ combine_kernel(const float* __restrict__ pm, const float* __restrict__ pl,
     if (out_m != nullptr) {
       static_cast<float*>(out)[row * out_row + e] = o;
       if (e == 0) {
-        out_m[row] = m;
-        out_l[row] = l;
+        out_m[row * out_ml] = m;
+        out_l[row * out_ml] = l;
       }
     } else {
       store_elem_rt(out, row * out_row + e, l > 0.0f ? o / l : 0.0f, out_dtype);
@@ -54,11 +54,11 @@ combine_kernel(const float* __restrict__ pm, const float* __restrict__ pl,
 
 int launch_combine(const float* pm, const float* pl, const float* po, int n_parts,
                    int64_t ml_row, int64_t ml_part, int64_t o_row, int64_t o_part, void* out,
-                   int out_dtype, int64_t out_row, float* out_m, float* out_l, int n_rows,
-                   int head_dim, cudaStream_t st) {
+                   int out_dtype, int64_t out_row, float* out_m, float* out_l, int64_t out_ml,
+                   int n_rows, int head_dim, cudaStream_t st) {
   if (n_rows == 0) return KNLP_OK;
   combine_kernel<<<n_rows, kThreads, 0, st>>>(pm, pl, po, n_parts, ml_row, ml_part, o_row, o_part,
-                                              out, out_dtype, out_row, out_m, out_l, head_dim);
+                                              out, out_dtype, out_row, out_m, out_l, out_ml, head_dim);
   return cudaGetLastError() == cudaSuccess ? KNLP_OK : KNLP_ERR_LAUNCH;
 }
 

@@ -105,7 +105,7 @@ int launch_decode_mma(const DecodeArgs& a, cudaStream_t st);
 
 int launch_combine(const float* pm, const float* pl, const float* po, int n_parts,
                    int64_t ml_row, int64_t ml_part, int64_t o_row, int64_t o_part, void* out,
-                   int out_dtype, int64_t out_row, float* out_m, float* out_l, int n_rows,
-                   int head_dim, cudaStream_t st);
+                   int out_dtype, int64_t out_row, float* out_m, float* out_l, int64_t out_ml,
+                   int n_rows, int head_dim, cudaStream_t st);
 
 }  // namespace knlp

@@ -270,7 +270,7 @@ def combine_partials(pm: torch.Tensor, pl: torch.Tensor, po: torch.Tensor,
         with torch.cuda.device(dev):
             rc = lib.knlp_b200_combine(pm.data_ptr(), pl.data_ptr(), po.data_ptr(), n_parts,
                                        ml_row, ml_part, o_row, o_part, oo.data_ptr(), _lib.F32, d,
-                                       om.data_ptr(), ol.data_ptr(), n_rows, d, _stream(dev))
+                                       om.data_ptr(), ol.data_ptr(), 1, n_rows, d, _stream(dev))
         _lib.check(rc, "knlp_b200_combine")
         return om, ol, oo
     if out is None:
@@ -280,7 +280,51 @@ def combine_partials(pm: torch.Tensor, pl: torch.Tensor, po: torch.Tensor,
     with torch.cuda.device(dev):
         rc = lib.knlp_b200_combine(pm.data_ptr(), pl.data_ptr(), po.data_ptr(), n_parts,
                                    ml_row, ml_part, o_row, o_part, out.data_ptr(), _DT[out.dtype],
-                                   d, None, None, n_rows, d, _stream(dev))
+                                   d, None, None, 0, n_rows, d, _stream(dev))
+    _lib.check(rc, "knlp_b200_combine")
+    return out
+
+
+def combine_to_packed(pm: torch.Tensor, pl: torch.Tensor, po: torch.Tensor) -> torch.Tensor:
+    """Merge the splits of each row into ONE partial and return it packed as
+    fp32 rows [o (d, un-normalised), m, l] of shape [..., d + 2]: the buffer a rank
+    of a context shard sends in its single all-gather."""
+    dev = _need_cuda(pm, pl, po)
+    if not (pm.is_contiguous() and pl.is_contiguous() and po.is_contiguous()):
+        raise ValueError("partials must be contiguous")
+    d = po.shape[-1]
+    n_parts = pm.shape[-1]
+    rows_shape = tuple(pm.shape[:-1])
+    n_rows = pm.numel() // max(n_parts, 1)
+    packed = torch.empty(rows_shape + (d + 2,), dtype=torch.float32, device=dev)
+    base = packed.data_ptr()
+    with torch.cuda.device(dev):
+        rc = _lib.load().knlp_b200_combine(
+            pm.data_ptr(), pl.data_ptr(), po.data_ptr(), n_parts, n_parts, 1, n_parts * d, d,
+            base, _lib.F32, d + 2, base + 4 * d, base + 4 * (d + 1), d + 2, n_rows, d,
+            _stream(dev))
+    _lib.check(rc, "knlp_b200_combine")
+    return packed
+
+
+def combine_packed(gathered: torch.Tensor, out_dtype=torch.float32) -> torch.Tensor:
+    """Final merge of packed partials gathered from all ranks: ``gathered`` is
+    [n_ranks, ..., d + 2] (rows as written by ``combine_to_packed``); returns the
+    normalised attention output [..., d]."""
+    dev = _need_cuda(gathered)
+    if not gathered.is_contiguous() or gathered.dtype != torch.float32:
+        raise ValueError("gathered partials must be a contiguous fp32 tensor")
+    n_parts = gathered.shape[0]
+    d = gathered.shape[-1] - 2
+    rows_shape = tuple(gathered.shape[1:-1])
+    n_rows = gathered[0].numel() // (d + 2)
+    out = torch.empty(rows_shape + (d,), dtype=out_dtype, device=dev)
+    base = gathered.data_ptr()
+    part = n_rows * (d + 2)
+    with torch.cuda.device(dev):
+        rc = _lib.load().knlp_b200_combine(
+            base + 4 * d, base + 4 * (d + 1), base, n_parts, d + 2, part, d + 2, part,
+            out.data_ptr(), _DT[out.dtype], d, None, None, 0, n_rows, d, _stream(dev))
     _lib.check(rc, "knlp_b200_combine")
     return out
 

@@ -91,10 +91,10 @@ def test_argument_errors_are_reported_on_the_host(lib):
     assert lib.knlp_b200_quant_append(null, null, null, null, 0, null, null, null, 5, 1, 64, 16,
                                       0.0, null) == 0
     # combine
-    assert lib.knlp_b200_combine(null, null, null, 1, 1, 1, 1, 1, null, 0, 1, null, null, 1, 64,
+    assert lib.knlp_b200_combine(null, null, null, 1, 1, 1, 1, 1, null, 0, 1, null, null, 0, 1, 64,
                                  null) == -1
-    assert lib.knlp_b200_combine(p, p, p, 0, 1, 1, 1, 1, p, 0, 1, null, null, 1, 64, null) == -2
-    assert lib.knlp_b200_combine(p, p, p, 1, 1, 1, 1, 1, p, 1, 1, p, p, 1, 64, null) == -3
+    assert lib.knlp_b200_combine(p, p, p, 0, 1, 1, 1, 1, p, 0, 1, null, null, 0, 1, 64, null) == -2
+    assert lib.knlp_b200_combine(p, p, p, 1, 1, 1, 1, 1, p, 1, 1, p, p, 1, 1, 64, null) == -3
 
 
 def test_decode_plan_fills_waves(lib):
