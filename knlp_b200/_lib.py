@@ -10,7 +10,8 @@ import ctypes as C
 import os
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libknlp_b200.so")
+# KNLP_B200_LIB points the binding at another build of the same library.
+LIB_PATH = os.environ.get("KNLP_B200_LIB") or os.path.join(_PKG, "libknlp_b200.so")
 
 ABI_VERSION = 1
 

@@ -49,7 +49,10 @@ namespace {
 
 constexpr int kWarpsCta = 8;
 constexpr int kThreads = kWarpsCta * 32;
-constexpr int kStages = 4;
+#ifndef KNLP_STAGES
+#define KNLP_STAGES 4
+#endif
+constexpr int kStages = KNLP_STAGES;
 constexpr int kRows = kWarpsCta * 16;  // (token, head) rows per stage
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -286,6 +289,7 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp) {
       // every lane of column fr now holds the full group sum; fetch columns 2ft, 2ft+1
       qsum[g][0] = __shfl_sync(0xffffffffu, s, (2 * ft) * 4) * kTwoM24;
       qsum[g][1] = __shfl_sync(0xffffffffu, s, (2 * ft + 1) * 4) * kTwoM24;
+      if constexpr (SPLIT) qsum[g][0] += qsum[g][1];  // hi + lo of head ft
     }
   }
   // scores leave the MMA scaled by 2^-24; softmax runs in the log2 domain
@@ -358,6 +362,7 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp) {
       }
     }
     // scale / zero rows: sub 0 copies the K side, sub 1 the V side
+#ifndef KNLP_EXP_NOSCALECOPY
     {
       const int sb = live ? G::SB : 0;
       const __half* ssrc = s_src0 + (static_cast<uint64_t>(blk) * sss0 + off * sss1);
@@ -375,6 +380,7 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp) {
         }
       }
     }
+#endif
   };
 
   const int n_iters = (end - start + TT - 1) / TT;
@@ -419,8 +425,15 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp) {
   const int Rbase = warp * 16;
   const uint32_t k_lm0 = smem_base + G::kOffK + (Rbase + lm_row) * G::KB;
   const uint32_t v_lm0 = smem_base + G::kOffV + (Rbase + lm_row) * G::VB;
-  const int k_lm_swz = swz<G::KCH>(lm_row);
-  const int v_lm_swz = swz<G::VCH>(lm_row);
+  // piece offsets of the ldmatrix calls (piece index xor row swizzle), fixed per thread
+  constexpr int kKLoads = kInt8K ? NG : NG / 2;
+  uint32_t k_lm[kKLoads], v_lm[NG / 2];
+#pragma unroll
+  for (int i = 0; i < kKLoads; ++i)
+    k_lm[i] = k_lm0 + (((2 * i + lm_q) ^ swz<G::KCH>(lm_row)) << 4);
+#pragma unroll
+  for (int i = 0; i < NG / 2; ++i)
+    v_lm[i] = v_lm0 + (((2 * i + lm_q) ^ swz<G::VCH>(lm_row)) << 4);
   // scale / zero rows of this thread's two accumulator rows (fr and fr + 8)
   const int sc_row0 = (Rbase + fr) * G::SB;
 
@@ -429,7 +442,11 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp) {
     __syncthreads();
     {
       const int nx = it + kStages - 1;
+#ifdef KNLP_EXP_NOCOPY
+      if (false) {
+#else
       if (nx < n_iters) {
+#endif
         issue_stage(nx, blk_next);
         blk_next = page_of(start + (nx + 1) * TT + c_tt);
       }
@@ -440,6 +457,10 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp) {
     const uint8_t* st = smem + stage_off;
     const int tok0 = start + it * TT + w_tile * 16;  // first token of this warp's tile
     if (tok0 >= end) continue;                        // whole tile past the end (warp-uniform)
+#ifdef KNLP_EXP_NOCOMPUTE
+    if (st[tid] == 255 && st[tid + 999] == 254) oacc[0][0][0] += 1.0f;
+    continue;
+#endif
 
     // ---------------- scores ----------------
     float sacc[NG][4];
@@ -448,13 +469,11 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) sacc[g][i] = 0.0f;
     {
-      const uint32_t kbase = k_lm0 + stage_off;
       if constexpr (kInt8K) {
 #pragma unroll
         for (int g = 0; g < NG; ++g) {
           uint32_t w[4];
-          const int q = 2 * g + lm_q;
-          ldmatrix_x4(kbase + ((q ^ k_lm_swz) << 4), w);
+          ldmatrix_x4(k_lm[g] + stage_off, w);
           // w0: rows 0-7 piece 2g; w1: rows 8-15 piece 2g; w2/w3: piece 2g+1
           uint32_t lo0[2], hi0[2], lo1[2], hi1[2];
           unpack_int8x4(w[0], lo0);
@@ -468,8 +487,7 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp) {
 #pragma unroll
         for (int gp = 0; gp < NG / 2; ++gp) {
           uint32_t w[4];
-          const int q = 2 * gp + lm_q;
-          ldmatrix_x4(kbase + ((q ^ k_lm_swz) << 4), w);
+          ldmatrix_x4(k_lm[gp] + stage_off, w);
           // w0: rows 0-7 group 2gp; w1: rows 8-15 group 2gp; w2/w3: group 2gp+1
 #pragma unroll
           for (int s = 0; s < 2; ++s) {
@@ -514,17 +532,23 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp) {
           for (int g = 0; g < NG; ++g) kz[g] = (kInt8K ? -128.0f : -8.0f) * ks[g];
         }
         float c0 = 0.0f, c1 = 0.0f;  // columns 2ft, 2ft+1 (still scaled by 2^-24)
-#pragma unroll
-        for (int g = 0; g < NG; ++g) {
-          c0 = fmaf(ks[g], sacc[g][2 * rh], c0);
-          c1 = fmaf(ks[g], sacc[g][2 * rh + 1], c1);
-          c0 = fmaf(kz[g], qsum[g][0], c0);
-          c1 = fmaf(kz[g], qsum[g][1], c1);
-        }
         const bool valid = (tok0 + fr + rh * 8) < end;
         if constexpr (SPLIT) {
+          // hi and lo columns of one head share scale and zero: add them first
+#pragma unroll
+          for (int g = 0; g < NG; ++g) {
+            c0 = fmaf(ks[g], sacc[g][2 * rh] + sacc[g][2 * rh + 1], c0);
+            c1 = fmaf(kz[g], qsum[g][0], c1);
+          }
           sc[rh][0] = valid ? (c0 + c1) * score_mul : -INFINITY;
         } else {
+#pragma unroll
+          for (int g = 0; g < NG; ++g) {
+            c0 = fmaf(ks[g], sacc[g][2 * rh], c0);
+            c1 = fmaf(ks[g], sacc[g][2 * rh + 1], c1);
+            c0 = fmaf(kz[g], qsum[g][0], c0);
+            c1 = fmaf(kz[g], qsum[g][1], c1);
+          }
           sc[rh][0] = valid ? c0 * score_mul : -INFINITY;
           sc[rh][1] = valid ? c1 * score_mul : -INFINITY;
         }
@@ -595,12 +619,10 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp) {
         for (int g = 0; g < NG; ++g) zacc[g][h] = fmaf(pr[rh][h], vz[g], zacc[g][h]);
     }
 
-    const uint32_t vbase = v_lm0 + stage_off;
 #pragma unroll
     for (int gp = 0; gp < NG / 2; ++gp) {
       uint32_t w[4];
-      const int q = 2 * gp + lm_q;
-      ldmatrix_x4_trans(vbase + ((q ^ v_lm_swz) << 4), w);
+      ldmatrix_x4_trans(v_lm[gp] + stage_off, w);
       // w0: tokens 0-7 group 2gp; w1: tokens 8-15 group 2gp; w2/w3: group 2gp+1
 #pragma unroll
       for (int s = 0; s < 2; ++s) {
