@@ -74,9 +74,19 @@ typedef struct {
 
 /* Flags for knlp_b200_decode_splitk. */
 #define KNLP_DECODE_FORCE_GENERIC 1u /* use the stride-generic CUDA-core kernel */
+#define KNLP_DECODE_USE_TMA 2u       /* stage with TMA tensor copies + mbarriers instead of cp.async */
 
 /* ABI version of the loaded library (KNLP_B200_ABI_VERSION at build time). */
 int knlp_b200_abi_version(void);
+
+/*
+ * Debug aid, no counterpart in the reference.  The decode kernel bounds every
+ * barrier wait; if one ever runs out it sets a device-side status word and ends
+ * (its partials are then garbage).  This call SYNCHRONISES the current device,
+ * returns the word (0 = clean, 1 = a wait ran out, -1 = could not be read) and
+ * clears it.  Not for use on a hot path or during stream capture.
+ */
+int knlp_b200_debug_status(void);
 
 /* Static description of a knlp_status. */
 const char* knlp_b200_strerror(int status);

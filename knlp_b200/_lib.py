@@ -19,9 +19,11 @@ ABI_VERSION = 1
 F32, F16, BF16 = 0, 1, 2
 KV_NONE, KV_INT4_SYM, KV_INT4_ASYM, KV_INT8_G32 = 0, 1, 2, 3
 DECODE_FORCE_GENERIC = 1
+DECODE_USE_TMA = 2
 
 SYMBOLS = (
     "knlp_b200_abi_version",
+    "knlp_b200_debug_status",
     "knlp_b200_strerror",
     "knlp_b200_quant_append",
     "knlp_b200_decode_plan",
@@ -65,6 +67,8 @@ def load() -> C.CDLL:
     PL = C.POINTER(KvPlane)
     lib.knlp_b200_abi_version.restype = C.c_int
     lib.knlp_b200_abi_version.argtypes = []
+    lib.knlp_b200_debug_status.restype = C.c_int
+    lib.knlp_b200_debug_status.argtypes = []
     lib.knlp_b200_strerror.restype = C.c_char_p
     lib.knlp_b200_strerror.argtypes = [C.c_int]
     lib.knlp_b200_quant_append.restype = C.c_int

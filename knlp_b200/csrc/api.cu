@@ -53,6 +53,8 @@ extern "C" {
 
 int knlp_b200_abi_version(void) { return KNLP_B200_ABI_VERSION; }
 
+int knlp_b200_debug_status(void) { return read_and_clear_decode_status(); }
+
 const char* knlp_b200_strerror(int status) {
   switch (status) {
     case KNLP_OK: return "ok";
@@ -180,7 +182,7 @@ int knlp_b200_decode_splitk(const void* query, int q_dtype, const int64_t q_stri
   a.part_o = part_o;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (!(flags & KNLP_DECODE_FORCE_GENERIC)) {
-    rc = launch_decode_mma(a, st);
+    rc = launch_decode_mma(a, (flags & KNLP_DECODE_USE_TMA) != 0, st);
     if (rc <= 0) return rc;  // launched, or failed for good
   }
   return launch_decode_generic(a, st);

@@ -101,7 +101,10 @@ struct DecodeArgs {
 int launch_decode_generic(const DecodeArgs& a, cudaStream_t st);
 // Returns KNLP_OK if it launched, 1 if the shape/strides are not eligible for the
 // tensor-core kernel (caller falls back to the generic one), <0 on error.
-int launch_decode_mma(const DecodeArgs& a, cudaStream_t st);
+// allow_tma = false keeps the tensor-core kernel on its cp.async loader.
+int launch_decode_mma(const DecodeArgs& a, bool allow_tma, cudaStream_t st);
+// Device-side status word of the decode kernels (0 = clean); synchronises.
+int read_and_clear_decode_status();
 
 int launch_combine(const float* pm, const float* pl, const float* po, int n_parts,
                    int64_t ml_row, int64_t ml_part, int64_t o_row, int64_t o_part, void* out,

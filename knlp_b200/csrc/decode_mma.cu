@@ -42,9 +42,28 @@
 // Nothing in this kernel waits on another CTA or on an mbarrier: the only
 // synchronisation is cp.async group completion and __syncthreads.
 
+#include <cuda.h>
+
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <vector>
+
 #include "common.cuh"
 
 namespace knlp {
+
+// Set by a kernel whose bounded barrier wait ran out (never expected); read and
+// cleared by knlp_b200_debug_status().
+__device__ int g_decode_status = 0;
+
+int read_and_clear_decode_status() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_decode_status, sizeof(int)) != cudaSuccess) return -1;
+  if (v != 0) cudaMemcpyToSymbol(g_decode_status, &zero, sizeof(int));
+  return v;
+}
+
 namespace {
 
 constexpr int kWarpsCta = 8;
@@ -60,6 +79,20 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
 }
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
+#if defined(KNLP_EXP_L2ONLY)
+  if (src_bytes) asm volatile("prefetch.global.L2 [%0];\n" ::"l"(src) : "memory");
+  return;
+#elif defined(KNLP_EXP_REGONLY)
+  if (src_bytes) {
+    uint32_t x, y, z, w;
+    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(x), "=r"(y), "=r"(z), "=r"(w)
+                 : "l"(src)
+                 : "memory");
+    asm volatile("" ::"r"(x), "r"(y), "r"(z), "r"(w));
+  }
+  return;
+#endif
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src),
                "r"(src_bytes)
                : "memory");
@@ -112,6 +145,77 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// ---- mbarrier + TMA (cp.async.bulk.tensor) primitives, CTA scope, no multicast ----
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+#ifdef KNLP_EXP_TESTWAIT
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+#else
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+#endif
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up after kSpinLimit polls (each poll itself blocks for a
+// hardware-defined time), so a lost completion ends the kernel instead of hanging it.
+constexpr int kSpinLimit = 1 << 20;
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (int i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, uint32_t bar, int c0,
+                                            int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5, %6}], [%2];\n" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, uint32_t bar, int c0,
+                                            int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5}], [%2];\n" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+// Tensor maps of one launch, passed by value as a __grid_constant__ parameter.
+// Every code box has 128-byte rows under the 128-byte swizzle, because shared-memory
+// fills are only efficient in whole 128-byte lines:
+//   k, v   wide (the CTA's heads of one token span >= 128 bytes): 4-D (128 bytes,
+//          128-byte columns of a token row, tokens of a page, blocks), box = one
+//          column x 16 tokens, i.e. 128/row_bytes adjacent heads per shared-memory row;
+//          narrow (they span < 128 bytes and the tokens of the CTA's heads are
+//          contiguous): 3-D (128 bytes, 128-byte rows of a page, blocks), box = the rows
+//          of 16 tokens, i.e. several tokens per shared-memory row
+//   ks..vz 3-D byte tensors of the scale / zero arrays; box = 16 tokens x the kv heads
+//          of the CTA, as [token][head] rows (scale_merged: the box is one contiguous run)
+struct alignas(64) TmaMaps {
+  CUtensorMap k, v, ks, kz, vs, vz;
+  int scale_merged;
+  int k_narrow, v_narrow;
+};
+
 __device__ __forceinline__ uint32_t pack_h2(__half lo, __half hi) {
   __half2 h = __halves2half2(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
@@ -147,7 +251,10 @@ __device__ __forceinline__ void unpack_int8x4(uint32_t w, uint32_t out[2]) {
   out[1] = __byte_perm(u, 0u, 0x4342);
 }
 
-template <int HD, int KMODE>
+// Shared-memory geometry of a stage.  PAD = 16 (cp.async path) separates the 16-row
+// code tiles of the eight warps by one extra 16-byte piece, so that a warp-wide copy
+// of one token row (all heads, 512 contiguous bytes) lands in distinct banks.
+template <int HD, int KMODE, int PAD>
 struct Geo {
   static constexpr bool kInt8K = (KMODE == KNLP_KV_INT8_G32);
   static constexpr int NG = HD / 32;
@@ -156,9 +263,11 @@ struct Geo {
   static constexpr int KCH = KB / 16;              // 16-byte pieces per K row
   static constexpr int VCH = VB / 16;
   static constexpr int SB = NG * 2;                // scale row bytes
+  static constexpr int kTileK = 16 * KB + PAD;     // one warp's 16 K rows
+  static constexpr int kTileV = 16 * VB + PAD;
   static constexpr int kOffK = 0;
-  static constexpr int kOffV = kOffK + kRows * KB;
-  static constexpr int kOffKs = kOffV + kRows * VB;
+  static constexpr int kOffV = kOffK + kWarpsCta * kTileK;
+  static constexpr int kOffKs = kOffV + kWarpsCta * kTileV;
   static constexpr int kOffKz = kOffKs + kRows * SB;
   static constexpr int kOffVs = kOffKz + kRows * SB;
   static constexpr int kOffVz = kOffVs + kRows * SB;
@@ -178,16 +287,28 @@ struct MmaParams {
   int page_log2;  // block_size = 1 << page_log2
 };
 
-template <int HD, int KMODE, int VMODE, bool SPLIT>
+// TMA = true: stages are filled by cp.async.bulk.tensor copies issued by one warp
+// per iteration (the warps take turns) and handed over through full/empty
+// mbarriers; the warps never meet at a CTA barrier inside the main loop.
+// TMA = false: stages are filled by cp.async from all threads (any 16-byte
+// aligned strides), one __syncthreads per stage.
+template <int HD, int KMODE, int VMODE, bool SPLIT, bool TMA>
 __global__ void __launch_bounds__(kThreads, 2)
-decode_mma_kernel(const DecodeArgs a, const MmaParams mp) {
-  using G = Geo<HD, KMODE>;
+decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant__ TmaMaps tm) {
+  using G = Geo<HD, KMODE, TMA ? 0 : 16>;
   constexpr int NG = G::NG;
   constexpr bool kInt8K = G::kInt8K;
   constexpr bool kAsymK = (KMODE == KNLP_KV_INT4_ASYM);
   constexpr bool kAsymV = (VMODE == KNLP_KV_INT4_ASYM);
 
-  extern __shared__ __align__(128) uint8_t smem[];
+#ifdef KNLP_EXP_TIMELINE
+  const long long tl_start = clock64();
+#endif
+  extern __shared__ uint8_t smem_raw[];
+  // swizzled TMA tiles need their natural alignment: round the base up to 1 KB
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  __shared__ __align__(8) uint64_t bars[2 * kStages];  // full[0..kStages), empty[...]
+  __shared__ int pg_tab[kStages + 1][16];              // page ids of the stages in flight
 
   const int tid = threadIdx.x;
   const int lane = tid & 31;
@@ -295,95 +416,308 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp) {
   // scores leave the MMA scaled by 2^-24; softmax runs in the log2 domain
   const float score_mul = rsqrtf(static_cast<float>(HD)) * 1.4426950408889634f * kTwo24;
 
-  // ---------------- copy role of this thread: half of one shared-memory row ----
-  // Row R of a stage belongs to consumer warp R / 16 (kv head (R/16) % HPB, token
-  // tile (R/16) / HPB) and is token R % 16 of that tile.  A warp of copiers fills
-  // the 16 rows of one consumer warp: contiguous in shared memory (conflict-free
-  // writes), 16 rows of one head in global memory (whole 32-byte sectors).
-  const int c_R = tid >> 1;
-  const int c_sub = tid & 1;
-  const int c_r16 = c_R & 15;
-  const int c_ws = c_R >> 4;
-  const int c_tt = ((c_ws >> hpb_log2) << 4) + c_r16;  // token within the stage
-  const int c_kvh = hb * HPB + (c_ws & (HPB - 1));
+  // ---------------- cp.async path: copy role of this thread ----------------
+  // The 16-byte pieces of a stage are dealt to the threads in MEMORY order (token,
+  // then head, then piece), so a warp-wide cp.async reads 512 contiguous bytes (the
+  // natural layout keeps the heads of a token adjacent) and, thanks to the 16-byte pad
+  // between the warps' tiles, writes them to distinct banks.  Piece i of a plane:
+  // token i / (HPB * CH), head (i / CH) % HPB, piece i % CH; a thread owns pieces
+  // tid, tid + 256, ...  (same head and piece, tokens 256 / (HPB * CH) apart).
   const int page_mask = (1 << mp.page_log2) - 1;
   const int32_t* bt_row = a.block_table + static_cast<int64_t>(seq) * a.bt_stride;
   const int max_blk = static_cast<int>(a.num_blocks) - 1;
-
-  const uint8_t* k_src0 = a.k.codes + c_kvh * a.k.cs[2] + c_sub * (G::KCH / 2) * 16;
-  const uint8_t* v_src0 = a.v.codes + c_kvh * a.v.cs[2] + c_sub * (G::VCH / 2) * 16;
-  const Plane& sp = c_sub ? a.v : a.k;
-  const __half* s_src0 = sp.scales + c_kvh * sp.ss[2];
-  const __half* z_src0 = sp.zeros ? sp.zeros + c_kvh * sp.zs[2] : nullptr;
+  const uint32_t smem_base = smem_u32(smem);
+  constexpr int kKPer = G::KCH / 2, kVPer = G::VCH / 2;  // pieces per thread and stage
+  constexpr int kKChLog = G::KCH == 8 ? 3 : G::KCH == 4 ? 2 : 1;
+  constexpr int kVChLog = G::VCH == 4 ? 2 : 1;
+  const int k_lg = hpb_log2 + kKChLog, v_lg = hpb_log2 + kVChLog;
+  const int k_tt0 = tid >> k_lg, v_tt0 = tid >> v_lg;       // token of piece 0 in the stage
+  const int k_dtt = kThreads >> k_lg, v_dtt = kThreads >> v_lg;  // token step between pieces
+  const int k_j = tid & ((1 << k_lg) - 1), v_j = tid & ((1 << v_lg) - 1);
+  const uint8_t* k_src0 = a.k.codes + (hb * (G::KB << hpb_log2) + k_j * 16);
+  const uint8_t* v_src0 = a.v.codes + (hb * (G::VB << hpb_log2) + v_j * 16);
   const uint32_t kcs0 = static_cast<uint32_t>(a.k.cs[0]), kcs1 = static_cast<uint32_t>(a.k.cs[1]);
   const uint32_t vcs0 = static_cast<uint32_t>(a.v.cs[0]), vcs1 = static_cast<uint32_t>(a.v.cs[1]);
-  const uint32_t sss0 = static_cast<uint32_t>(sp.ss[0]), sss1 = static_cast<uint32_t>(sp.ss[1]);
-  const uint32_t szs0 = static_cast<uint32_t>(sp.zs[0]), szs1 = static_cast<uint32_t>(sp.zs[1]);
-  const bool c_has_zero = c_sub ? kAsymV : kAsymK;
+  uint32_t k_dst[kKPer], v_dst[kVPer];
+#pragma unroll
+  for (int n = 0; n < kKPer; ++n) {
+    const int tt = k_tt0 + n * k_dtt, r = tt & 15;
+    const int ws = (k_j >> kKChLog) + ((tt >> 4) << hpb_log2);
+    k_dst[n] = smem_base + G::kOffK + ws * G::kTileK + r * G::KB +
+               (((k_j & (G::KCH - 1)) ^ swz<G::KCH>(r)) << 4);
+  }
+#pragma unroll
+  for (int n = 0; n < kVPer; ++n) {
+    const int tt = v_tt0 + n * v_dtt, r = tt & 15;
+    const int ws = (v_j >> kVChLog) + ((tt >> 4) << hpb_log2);
+    v_dst[n] = smem_base + G::kOffV + ws * G::kTileV + r * G::VB +
+               (((v_j & (G::VCH - 1)) ^ swz<G::VCH>(r)) << 4);
+  }
+  // Scales and zeros: each array of a stage is 128 rows of SB bytes laid out
+  // [token][head], also copied in 16-byte pieces in memory order; thread tid serves
+  // array tid / (8 * SB) (ks, kz, vs, vz), piece tid % (8 * SB).
+  constexpr int kSPieces = 8 * G::SB;  // per array and stage
+  const int s_arr = tid / kSPieces;
+  const int s_byte = (tid % kSPieces) * 16;        // byte offset inside the stage's array
+  const int s_tb = G::SB << hpb_log2;              // bytes of one token's row (CTA's heads)
+  const int s_tt = s_byte / s_tb;                  // (first) token of the piece
+  const bool s_on = s_arr < 4 && !((s_arr == 1 && !kAsymK) || (s_arr == 3 && !kAsymV));
+  const Plane& s_pl = (s_arr >= 2) ? a.v : a.k;
+  const bool s_zero = (s_arr & 1) != 0;
+  const __half* s_base = s_zero ? s_pl.zeros : s_pl.scales;
+  const int64_t* s_st = s_zero ? s_pl.zs : s_pl.ss;
+  const uint8_t* s_src0 = reinterpret_cast<const uint8_t*>(s_base) +
+                          (hb * s_tb + (s_tb >= 16 ? s_byte % s_tb : 0));
+  const uint32_t s_st0 = s_on ? static_cast<uint32_t>(s_st[0]) * 2 : 0;  // bytes
+  const uint32_t s_st1 = s_on ? static_cast<uint32_t>(s_st[1]) * 2 : 0;
+  const uint32_t s_dst =
+      smem_base + (s_arr == 0 ? G::kOffKs : s_arr == 1 ? G::kOffKz : s_arr == 2 ? G::kOffVs
+                                                                               : G::kOffVz) +
+      s_byte;
 
-  const uint32_t smem_base = smem_u32(smem);
-  const uint32_t k_dst0 = smem_base + G::kOffK + c_R * G::KB;
-  const uint32_t v_dst0 = smem_base + G::kOffV + c_R * G::VB;
-  const uint32_t s_dst0 = smem_base + (c_sub ? G::kOffVs : G::kOffKs) + c_R * G::SB;
-  const uint32_t z_dst0 = smem_base + (c_sub ? G::kOffVz : G::kOffKz) + c_R * G::SB;
-  const int k_swz = swz<G::KCH>(c_r16);
-  const int v_swz = swz<G::VCH>(c_r16);
-
-  auto page_of = [&](int tok) -> uint32_t {
-    int b = (tok < end) ? __ldg(bt_row + (tok >> mp.page_log2)) : 0;
-    b = b < 0 ? 0 : (b > max_blk ? max_blk : b);
-    return static_cast<uint32_t>(b);
+  // Page ids reach the copiers through a small table in shared memory: 16 threads
+  // load the ids of a stage two iterations before it is issued and park them in a
+  // register for one iteration, so no instruction ever waits on the page-table load.
+  auto load_pages = [&](int st_it) -> int {  // raw id of page `tid` of stage st_it
+    const int p = ((start + st_it * TT) >> mp.page_log2) + tid;
+    int b = 0;
+    if (tid < 16 && (p << mp.page_log2) < end) b = __ldg(bt_row + p);
+    return b;
+  };
+  auto page_id = [&](int slot, int tok, int page0) -> uint32_t {
+    const int raw = pg_tab[slot][(tok >> mp.page_log2) - page0];
+    return static_cast<uint32_t>(raw < 0 ? 0 : (raw > max_blk ? max_blk : raw));
   };
 
-  auto issue_stage = [&](int it, uint32_t blk) {
-    const int tok = start + it * TT + c_tt;
-    const bool live = tok < end;
-    const int nbytes = live ? 16 : 0;  // 0 -> zero fill, source not read
-    const uint32_t off = static_cast<uint32_t>(tok & page_mask);
+#ifdef KNLP_EXP_TIMELINE
+  long long tl_cp = 0, tl_first = 0, tl_addr = 0, tl_is0 = 0, tl_pg = 0;
+#endif
+  constexpr int kPiecesAll = kKPer + kVPer + 1;
+  uint4 st_regs[kPiecesAll];
+  uint32_t st_dsts[kPiecesAll];
+  bool st_pending = false;
+  auto flush_pending = [&]() {
+    if (st_pending) {
+#pragma unroll
+      for (int n = 0; n < kPiecesAll; ++n) {
+#ifdef KNLP_EXP_NOSTS
+        // consume the loaded registers with a real instruction, but write nothing
+        if ((st_regs[n].x ^ st_regs[n].y ^ st_regs[n].z ^ st_regs[n].w) == 0x9e3779b9u &&
+            st_dsts[n] == 1u)
+          a.part_l[0] = 1.0f;
+        continue;
+#endif
+        if (n < kPiecesAll - 1 || s_on)
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(st_dsts[n]),
+                       "r"(st_regs[n].x), "r"(st_regs[n].y), "r"(st_regs[n].z), "r"(st_regs[n].w)
+                       : "memory");
+      }
+      st_pending = false;
+    }
+  };
+  auto issue_stage = [&](int it) {
+    const int stage_tok0 = start + it * TT;
+    const int page0 = stage_tok0 >> mp.page_log2;
+    const int slot = it % (kStages + 1);
+#ifdef KNLP_EXP_READSLOT0
+    const uint32_t stage_off = static_cast<uint32_t>(it % kStages == 0 ? 1 : it % kStages) * G::kStageBytes;
+#else
     const uint32_t stage_off = static_cast<uint32_t>(it % kStages) * G::kStageBytes;
-    {
-      const uint8_t* src = k_src0 + (static_cast<uint64_t>(blk) * kcs0 + off * kcs1);
-      const uint32_t dst = k_dst0 + stage_off;
-      constexpr int per = G::KCH / 2;
+#endif
+    constexpr int kPieces = kKPer + kVPer + 1;
+    const uint8_t* srcs[kPieces];
+    uint32_t dsts[kPieces];
+    bool lives[kPieces];
 #pragma unroll
-      for (int j = 0; j < per; ++j) {
-        const int q = c_sub * per + j;
-        cp_async16(dst + ((q ^ k_swz) << 4), src + (j << 4), nbytes);
-      }
+    for (int n = 0; n < kKPer; ++n) {
+      const int tok = stage_tok0 + k_tt0 + n * k_dtt;
+      lives[n] = tok < end;
+      const uint32_t blk = lives[n] ? page_id(slot, tok, page0) : 0u;
+      srcs[n] =
+          k_src0 + (static_cast<uint64_t>(blk) * kcs0 + static_cast<uint32_t>(tok & page_mask) * kcs1);
+      dsts[n] = k_dst[n] + stage_off;
     }
-    {
-      const uint8_t* src = v_src0 + (static_cast<uint64_t>(blk) * vcs0 + off * vcs1);
-      const uint32_t dst = v_dst0 + stage_off;
-      constexpr int per = G::VCH / 2;
 #pragma unroll
-      for (int j = 0; j < per; ++j) {
-        const int q = c_sub * per + j;
-        cp_async16(dst + ((q ^ v_swz) << 4), src + (j << 4), nbytes);
-      }
+    for (int n = 0; n < kVPer; ++n) {
+      const int tok = stage_tok0 + v_tt0 + n * v_dtt;
+      lives[kKPer + n] = tok < end;
+      const uint32_t blk = lives[kKPer + n] ? page_id(slot, tok, page0) : 0u;
+      srcs[kKPer + n] =
+          v_src0 + (static_cast<uint64_t>(blk) * vcs0 + static_cast<uint32_t>(tok & page_mask) * vcs1);
+      dsts[kKPer + n] = v_dst[n] + stage_off;
     }
-    // scale / zero rows: sub 0 copies the K side, sub 1 the V side
-#ifndef KNLP_EXP_NOSCALECOPY
     {
-      const int sb = live ? G::SB : 0;
-      const __half* ssrc = s_src0 + (static_cast<uint64_t>(blk) * sss0 + off * sss1);
-      if constexpr (G::SB == 8) {
-        cp_async8(s_dst0 + stage_off, ssrc, sb);
-      } else {
-        cp_async4(s_dst0 + stage_off, ssrc, sb);
-      }
-      if (c_has_zero) {
-        const __half* zsrc = z_src0 + (static_cast<uint64_t>(blk) * szs0 + off * szs1);
-        if constexpr (G::SB == 8) {
-          cp_async8(z_dst0 + stage_off, zsrc, sb);
-        } else {
-          cp_async4(z_dst0 + stage_off, zsrc, sb);
-        }
-      }
+      const int tok = stage_tok0 + s_tt;
+      lives[kPieces - 1] = s_on && tok < end;
+      const uint32_t blk = lives[kPieces - 1] ? page_id(slot, tok, page0) : 0u;
+      srcs[kPieces - 1] =
+          s_src0 + (static_cast<uint64_t>(blk) * s_st0 + static_cast<uint32_t>(tok & page_mask) * s_st1);
+      dsts[kPieces - 1] = s_dst + stage_off;
     }
+#if defined(KNLP_DEFER_COPY)
+#pragma unroll
+    for (int n = 0; n < kPieces; ++n) {
+      st_regs[n] = make_uint4(0u, 0u, 0u, 0u);
+      st_dsts[n] = dsts[n];
+      if (lives[n])
+        asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                     : "=r"(st_regs[n].x), "=r"(st_regs[n].y), "=r"(st_regs[n].z),
+                       "=r"(st_regs[n].w)
+                     : "l"(srcs[n]));
+    }
+    st_pending = true;
+#elif defined(KNLP_SYNC_COPY)
+    // global -> registers -> shared: the warp waits for its own loads (the other
+    // warps keep the SM busy meanwhile)
+    uint4 regs[kPieces];
+#pragma unroll
+    for (int n = 0; n < kPieces; ++n) {
+      regs[n] = make_uint4(0u, 0u, 0u, 0u);
+      if (lives[n])
+        asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                     : "=r"(regs[n].x), "=r"(regs[n].y), "=r"(regs[n].z), "=r"(regs[n].w)
+                     : "l"(srcs[n]));
+    }
+#pragma unroll
+    for (int n = 0; n < kPieces; ++n) {
+      if (n < kPieces - 1 || s_on)
+        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(dsts[n]), "r"(regs[n].x),
+                     "r"(regs[n].y), "r"(regs[n].z), "r"(regs[n].w)
+                     : "memory");
+    }
+#else
+#ifdef KNLP_EXP_TIMELINE
+#pragma unroll
+    for (int n = 0; n < kPieces; ++n) asm volatile("" ::"l"(srcs[n]), "r"(dsts[n]) : "memory");
+    const long long ta = clock64();
+    tl_addr += ta - tl_is0;
+#endif
+#pragma unroll
+    for (int n = 0; n < kPieces; ++n) {
+      if (n < kPieces - 1 || s_on) cp_async16(dsts[n], srcs[n], lives[n] ? 16 : 0);  // 0 -> zero fill
+#ifdef KNLP_EXP_TIMELINE
+      if (n == 0) tl_first += clock64() - ta;
+#endif
+    }
+#ifdef KNLP_EXP_TIMELINE
+    tl_cp += clock64() - ta;
+#endif
 #endif
   };
 
   const int n_iters = (end - start + TT - 1) / TT;
+
+  // ---------------- TMA path: one warp fills a whole stage ----------------
+  const uint32_t bar0 = smem_u32(bars);
+  const int tiles = kWarpsCta >> hpb_log2;  // 16-token tiles per stage
+  constexpr int kScaleArrays = 2 + (kAsymK ? 1 : 0) + (kAsymV ? 1 : 0);
+  // bytes one live tile (16 tokens x HPB heads) brings into a stage
+  const uint32_t tile_bytes =
+      static_cast<uint32_t>((16 * (G::KB + G::VB) + kScaleArrays * 16 * G::SB) << hpb_log2);
+  // Shared-memory placement of the code tiles under TMA.  seg = bytes the CTA's heads
+  // take in one token row.  Wide (seg >= 128): one box per 128-byte column, rows =
+  // tokens.  Narrow: one box per tile, a row holds 128 / seg tokens.
+  const int k_seg = G::KB << hpb_log2, v_seg = G::VB << hpb_log2;
+  const int k_box = k_seg >= 128 ? k_seg >> 7 : 1, v_box = v_seg >= 128 ? v_seg >> 7 : 1;
+  // byte offset, inside the K or V region of a stage, of 16-byte piece q of token t of
+  // (head hl, tile tl), after the 128-byte swizzle
+  auto code_off = [&](int row_bytes, int seg, int nbox, int tl, int hl, int t, int q) -> int {
+    if (seg >= 128) {
+      const int hoff = hl * row_bytes;
+      const int c = ((hoff & 127) >> 4) + q;
+      return ((tl * nbox + (hoff >> 7)) << 11) + t * 128 + ((c ^ (t & 7)) << 4);
+    }
+    const int off = t * seg + hl * row_bytes + q * 16;
+    const int rho = off >> 7;
+    return tl * 16 * seg + rho * 128 + ((((off >> 4) & 7) ^ (rho & 7)) << 4);
+  };
+
+  // Page ids for the stage this warp fills NEXT (8 iterations from now) are loaded at
+  // the end of the current fill, so that a fill never waits on the page table.
+  int pg_pref[2] = {0, 0};
+  int pg_pref_it = -1;
+  const int nk = tiles * k_box, nv = tiles * v_box;  // K and V boxes per stage
+  const int n_copies = nk + nv + 4 * tiles;
+  auto tile_of_copy = [&](int c) -> int {
+    if (c < nk) return c / k_box;
+    if (c < nk + nv) return (c - nk) / v_box;
+    return (c - nk - nv) & (tiles - 1);
+  };
+  auto issue_tma = [&](int it) {
+    const int sn = it % kStages;
+    const int stage_tok0 = start + it * TT;
+    const int live_tiles = min(tiles, (end - stage_tok0 + 15) >> 4);
+    const uint32_t full = bar0 + sn * 8;
+    if (lane == 0) mbar_arrive_expect_tx(full, static_cast<uint32_t>(live_tiles) * tile_bytes);
+    __syncwarp();
+    const uint32_t stage_base = smem_base + static_cast<uint32_t>(sn) * G::kStageBytes;
+    // a lane owns copies lane and lane + 32 of the stage's boxes
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int c = lane + 32 * j;
+      if (c >= n_copies) continue;
+      const int tl = tile_of_copy(c);
+      if (tl >= live_tiles) continue;
+      const int tok = stage_tok0 + tl * 16;
+      int blk = (pg_pref_it == it) ? pg_pref[j] : __ldg(bt_row + (tok >> mp.page_log2));
+      blk = blk < 0 ? 0 : (blk > max_blk ? max_blk : blk);
+      const int off = tok & page_mask;
+      if (c < nk + nv) {
+        const bool is_v = c >= nk;
+        const int cc = is_v ? c - nk : c;
+        const int nbox = is_v ? v_box : k_box;
+        const int seg = is_v ? v_seg : k_seg;
+        const int col = cc % nbox;
+        const void* map = is_v ? static_cast<const void*>(&tm.v) : static_cast<const void*>(&tm.k);
+        const uint32_t region = stage_base + (is_v ? G::kOffV : G::kOffK);
+#ifdef KNLP_EXP_BULKROWS
+        if (seg == 512) {
+          const Plane& pl = is_v ? a.v : a.k;
+          for (int r = 0; r < 4; ++r) {
+            const int t = col * 4 + r;
+            const uint8_t* src = pl.codes + static_cast<int64_t>(blk) * pl.cs[0] +
+                                 static_cast<int64_t>(off + t) * pl.cs[1] + hb * seg;
+            asm volatile(
+                "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], "
+                "%2, [%3];\n" ::"r"(region + (tl * 16 + t) * 512),
+                "l"(src), "r"(512), "r"(full)
+                : "memory");
+          }
+        } else
+#endif
+        if (seg >= 128) {
+          tma_load_4d(region + ((tl * nbox + col) << 11), map, full, 0,
+                      ((hb * seg) >> 7) + col, off, blk);
+        } else {
+          tma_load_3d(region + tl * 16 * seg, map, full, 0, (off * seg) >> 7, blk);
+        }
+      } else {
+        const int arr = (c - nk - nv) / tiles;  // 0 ks, 1 kz, 2 vs, 3 vz
+        if ((arr == 1 && !kAsymK) || (arr == 3 && !kAsymV)) continue;
+        const void* map = arr == 0 ? &tm.ks : arr == 1 ? &tm.kz : arr == 2 ? &tm.vs : &tm.vz;
+        const int aoff =
+            arr == 0 ? G::kOffKs : arr == 1 ? G::kOffKz : arr == 2 ? G::kOffVs : G::kOffVz;
+        const uint32_t dst = stage_base + aoff + ((tl * 16 * G::SB) << hpb_log2);
+        if (tm.scale_merged) {
+          tma_load_3d(dst, map, full, ((off * G::SB) << hpb_log2) >> 2, 0, blk);
+        } else {
+          tma_load_3d(dst, map, full, hb * HPB * G::SB, off, blk);
+        }
+      }
+    }
+    // prefetch the page ids of this warp's next fill
+    const int nit = it + kWarpsCta;
+    pg_pref_it = nit;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int c = lane + 32 * j;
+      pg_pref[j] = 0;
+      if (c < n_copies) {
+        const int tok = start + nit * TT + tile_of_copy(c) * 16;
+        if (tok < end) pg_pref[j] = __ldg(bt_row + (tok >> mp.page_log2));
+      }
+    }
+  };
 
   // ---------------- accumulators ----------------
   // oacc[g][j]: output rows d = 32g + 4fr + 2j (c0, c1; scaled 2^-24) and
@@ -409,58 +743,164 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp) {
   }
 
   // ---------------- prologue: fill kStages-1 stages ----------------
-  uint32_t blk_next = page_of(start + c_tt);
+  int pg_reg = 0;  // cp.async path: page id parked by threads 0..15 (see load_pages)
+  bool lost = false;  // a bounded barrier wait ran out
+  if constexpr (TMA) {
+    if (tid == 0) {
 #pragma unroll
-  for (int s = 0; s < kStages - 1; ++s) {
-    if (s < n_iters) {
-      issue_stage(s, blk_next);
-      blk_next = page_of(start + (s + 1) * TT + c_tt);
+      for (int s = 0; s < kStages; ++s) {
+        mbar_init(bar0 + s * 8, 1);                        // full: the issuing lane + tx bytes
+        mbar_init(bar0 + (kStages + s) * 8, kWarpsCta);    // empty: one arrival per warp
+      }
+      asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    cp_async_commit();
+    __syncthreads();
+    if (warp == 0) {
+      for (int s = 0; s < kStages - 1 && s < n_iters; ++s) issue_tma(s);
+    }
+  } else {
+    if (tid < 16) {
+#pragma unroll
+      for (int s = 0; s < kStages; ++s) pg_tab[s][tid] = load_pages(s);
+      pg_reg = load_pages(kStages);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int s = 0; s < kStages - 1; ++s) {
+      if (s < n_iters) issue_stage(s);
+#ifdef KNLP_DEFER_COPY
+      flush_pending();
+#endif
+      cp_async_commit();
+    }
   }
 
   // ldmatrix source row of this lane: row (lane & 7) + 8 * ((lane >> 3) & 1), piece + (lane >> 4)
   const int lm_row = (lane & 7) + ((lane >> 3) & 1) * 8;
   const int lm_q = lane >> 4;
   const int Rbase = warp * 16;
-  const uint32_t k_lm0 = smem_base + G::kOffK + (Rbase + lm_row) * G::KB;
-  const uint32_t v_lm0 = smem_base + G::kOffV + (Rbase + lm_row) * G::VB;
+  const uint32_t k_lm0 = smem_base + G::kOffK + warp * G::kTileK + lm_row * G::KB;
+  const uint32_t v_lm0 = smem_base + G::kOffV + warp * G::kTileV + lm_row * G::VB;
   // piece offsets of the ldmatrix calls (piece index xor row swizzle), fixed per thread
   constexpr int kKLoads = kInt8K ? NG : NG / 2;
   uint32_t k_lm[kKLoads], v_lm[NG / 2];
 #pragma unroll
-  for (int i = 0; i < kKLoads; ++i)
-    k_lm[i] = k_lm0 + (((2 * i + lm_q) ^ swz<G::KCH>(lm_row)) << 4);
+  for (int i = 0; i < kKLoads; ++i) {
+    if constexpr (TMA) {
+      k_lm[i] = smem_base + G::kOffK +
+                code_off(G::KB, k_seg, k_box, w_tile, w_head, lm_row, 2 * i + lm_q);
+    } else {
+      k_lm[i] = k_lm0 + (((2 * i + lm_q) ^ swz<G::KCH>(lm_row)) << 4);
+    }
+  }
 #pragma unroll
-  for (int i = 0; i < NG / 2; ++i)
-    v_lm[i] = v_lm0 + (((2 * i + lm_q) ^ swz<G::VCH>(lm_row)) << 4);
+  for (int i = 0; i < NG / 2; ++i) {
+    if constexpr (TMA) {
+      v_lm[i] = smem_base + G::kOffV +
+                code_off(G::VB, v_seg, v_box, w_tile, w_head, lm_row, 2 * i + lm_q);
+    } else {
+      v_lm[i] = v_lm0 + (((2 * i + lm_q) ^ swz<G::VCH>(lm_row)) << 4);
+    }
+  }
   // scale / zero rows of this thread's two accumulator rows (fr and fr + 8)
-  const int sc_row0 = (Rbase + fr) * G::SB;
+  // scale / zero arrays of a stage are [token][head of the CTA] rows of SB bytes
+  const int sc_row0 = ((((w_tile << 4) + fr) << hpb_log2) + w_head) * G::SB;
+  const int sc_row8 = (8 * G::SB) << hpb_log2;
 
+#ifdef KNLP_EXP_TIMELINE
+  long long tl_wait = 0, tl_bar = 0, tl_body = 0, tl_prev = 0, tl_issue = 0, tl_flush = 0;
+  const long long tl_loop0 = clock64();
+#endif
   for (int it = 0; it < n_iters; ++it) {
-    cp_async_wait<kStages - 2>();
-    __syncthreads();
-    {
+    if constexpr (TMA) {
+      // the warps take turns refilling the slot that iteration it-1 released
       const int nx = it + kStages - 1;
+      if (warp == (it & (kWarpsCta - 1)) && nx < n_iters) {
+        if (nx >= kStages) {
+          const uint32_t par = static_cast<uint32_t>((nx / kStages) - 1) & 1u;
+          if (!mbar_wait(bar0 + (kStages + nx % kStages) * 8, par)) lost = true;
+        }
+        if (!lost) issue_tma(nx);
+      }
+      if (!mbar_wait(bar0 + (it % kStages) * 8, static_cast<uint32_t>(it / kStages) & 1u))
+        lost = true;
+      if (__any_sync(0xffffffffu, lost)) {
+        if (lane == 0) atomicExch(&g_decode_status, 1);
+        break;
+      }
+    } else {
+#ifdef KNLP_EXP_TIMELINE
+      const long long tlf = clock64();
+#endif
+#ifdef KNLP_DEFER_COPY
+      flush_pending();
+#endif
+#ifdef KNLP_EXP_TIMELINE
+      const long long tl0 = clock64();
+      tl_flush += tl0 - tlf;
+#endif
+#ifndef KNLP_EXP_NOWAIT
+      cp_async_wait<kStages - 2>();
+#endif
+#ifdef KNLP_EXP_TIMELINE
+      const long long tl1 = clock64();
+#endif
+      __syncthreads();
+#ifdef KNLP_EXP_TIMELINE
+      const long long tl2 = clock64();
+      tl_wait += tl1 - tl0;
+      tl_bar += tl2 - tl1;
+      if (it > 0) tl_body += tl0 - tl_prev;
+      tl_prev = tl2;
+#endif
+      if (tid < 16) {
+        pg_tab[(it + kStages) % (kStages + 1)][tid] = pg_reg;  // loaded one iteration ago
+        pg_reg = load_pages(it + kStages + 1);
+      }
+      const int nx = it + kStages - 1;
+#ifdef KNLP_EXP_TIMELINE
+      asm volatile("" ::: "memory");
+      tl_is0 = clock64();
+      tl_pg += tl_is0 - tl2;
+#endif
 #ifdef KNLP_EXP_NOCOPY
       if (false) {
 #else
       if (nx < n_iters) {
 #endif
-        issue_stage(nx, blk_next);
-        blk_next = page_of(start + (nx + 1) * TT + c_tt);
+        issue_stage(nx);
       }
       cp_async_commit();
+#ifdef KNLP_EXP_TIMELINE
+      tl_issue += clock64() - tl2;
+#endif
     }
 
+#ifdef KNLP_EXP_READSLOT0
+    const uint32_t stage_off = 0;
+#else
     const uint32_t stage_off = static_cast<uint32_t>(it % kStages) * G::kStageBytes;
+#endif
     const uint8_t* st = smem + stage_off;
     const int tok0 = start + it * TT + w_tile * 16;  // first token of this warp's tile
-    if (tok0 >= end) continue;                        // whole tile past the end (warp-uniform)
+    const uint32_t empty_bar = bar0 + (kStages + it % kStages) * 8;
+    if (tok0 >= end) {  // whole tile past the end (warp-uniform): nothing was loaded for it
+      if constexpr (TMA) {
+        if (lane == 0) mbar_arrive(empty_bar);
+      }
+      continue;
+    }
 #ifdef KNLP_EXP_NOCOMPUTE
     if (st[tid] == 255 && st[tid + 999] == 254) oacc[0][0][0] += 1.0f;
+    if constexpr (TMA) {
+      if (lane == 0) mbar_arrive(empty_bar);
+    }
     continue;
 #endif
+    // Rows past the end of a partial tile may hold whatever the page holds there (a TMA
+    // box is always whole; a 16-byte scale piece can span two tokens), so their scales
+    // are masked before use.
+    const bool partial = tok0 + 16 > end;
 
     // ---------------- scores ----------------
     float sacc[NG][4];
@@ -510,7 +950,7 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp) {
       for (int rh = 0; rh < 2; ++rh) {
         float ks[NG], kz[NG];
         const __half2* sp2 =
-            reinterpret_cast<const __half2*>(st + G::kOffKs + sc_row0 + rh * 8 * G::SB);
+            reinterpret_cast<const __half2*>(st + G::kOffKs + sc_row0 + rh * sc_row8);
 #pragma unroll
         for (int g2 = 0; g2 < NG / 2; ++g2) {
           const float2 f = __half22float2(sp2[g2]);
@@ -519,7 +959,7 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp) {
         }
         if constexpr (kAsymK) {
           const __half2* zp2 =
-              reinterpret_cast<const __half2*>(st + G::kOffKz + sc_row0 + rh * 8 * G::SB);
+              reinterpret_cast<const __half2*>(st + G::kOffKz + sc_row0 + rh * sc_row8);
 #pragma unroll
           for (int g2 = 0; g2 < NG / 2; ++g2) {
             const float2 f = __half22float2(zp2[g2]);
@@ -587,12 +1027,13 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp) {
       }
     }
 
+#ifndef KNLP_EXP_NOPV
     // ---------------- P' = p * vscale per group, transposed into the B operand ----
     float vs[2][NG];
 #pragma unroll
     for (int rh = 0; rh < 2; ++rh) {
       const __half2* sp2 =
-          reinterpret_cast<const __half2*>(st + G::kOffVs + sc_row0 + rh * 8 * G::SB);
+          reinterpret_cast<const __half2*>(st + G::kOffVs + sc_row0 + rh * sc_row8);
       float vz[NG];
 #pragma unroll
       for (int g2 = 0; g2 < NG / 2; ++g2) {
@@ -602,7 +1043,7 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp) {
       }
       if constexpr (kAsymV) {
         const __half2* zp2 =
-            reinterpret_cast<const __half2*>(st + G::kOffVz + sc_row0 + rh * 8 * G::SB);
+            reinterpret_cast<const __half2*>(st + G::kOffVz + sc_row0 + rh * sc_row8);
 #pragma unroll
         for (int g2 = 0; g2 < NG / 2; ++g2) {
           const float2 f = __half22float2(zp2[g2]);
@@ -612,6 +1053,13 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp) {
       } else {
 #pragma unroll
         for (int g = 0; g < NG; ++g) vz[g] = -8.0f * vs[rh][g];
+      }
+      if (partial && (tok0 + fr + rh * 8) >= end) {
+#pragma unroll
+        for (int g = 0; g < NG; ++g) {
+          vs[rh][g] = 0.0f;
+          vz[g] = 0.0f;
+        }
       }
 #pragma unroll
       for (int h = 0; h < NH; ++h)
@@ -650,8 +1098,23 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp) {
         mma16816(oacc[g][1], e0[2], e0[3], e1[2], e1[3], pb[0], pb[1]);
       }
     }
+#endif
+    if constexpr (TMA) {
+      // this warp is done reading the stage: release its slot to the refilling warp
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty_bar);
+    }
   }
 
+#ifdef KNLP_EXP_TIMELINE
+  if (lane == 0 && blockIdx.x == 5 && blockIdx.z == 3)
+    printf("prologue %lld  loop %lld cycles; per iter: page block %lld  addr %lld\n", tl_loop0 - tl_start,
+           clock64() - tl_loop0, tl_pg / n_iters, tl_addr / n_iters);
+  if (lane == 0 && blockIdx.x == 5 && blockIdx.z == 3)
+    printf("warp %d iters %d: wait %lld  barrier %lld  body(issue+compute) %lld  issue %lld  flush %lld  cp.async x5 %lld  first %lld cycles per iter\n",
+           warp, n_iters, tl_wait / n_iters, tl_bar / n_iters, tl_body / max(n_iters - 1, 1),
+           tl_issue / n_iters, tl_flush / n_iters, tl_cp / n_iters, tl_first / n_iters);
+#endif
   // ---------------- epilogue: reduce lanes, merge the warps of a head, write ----
   cp_async_wait<0>();
   __syncthreads();  // all stages consumed; shared memory is reused below
@@ -719,7 +1182,6 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp) {
   __syncthreads();
 
   // merge: thread i handles (kv head hl, q head slot, element e)
-  const int tiles = kWarpsCta >> hpb_log2;
   const int total = HPB * n_rep * HD;
   for (int i = tid; i < total; i += kThreads) {
     const int e = i % HD;
@@ -751,16 +1213,188 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp) {
   }
 }
 
-template <int HD, int KMODE, int VMODE, bool SPLIT>
-int launch_inst(const DecodeArgs& a, const MmaParams& mp, cudaStream_t st) {
-  using G = Geo<HD, KMODE>;
-  auto kern = decode_mma_kernel<HD, KMODE, VMODE, SPLIT>;
+// ---------------------------------------------------------------- host side
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no libcuda link).
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) !=
+            cudaSuccess ||
+        q != cudaDriverEntryPointSuccess) {
+      cudaGetLastError();
+      p = nullptr;
+    }
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+bool encode(CUtensorMap* m, void* base, int rank, const cuuint64_t* dims,
+            const cuuint64_t* strides, const cuuint32_t* box, CUtensorMapSwizzle swz) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint32_t ones[5] = {1, 1, 1, 1, 1};
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, static_cast<cuuint32_t>(rank), base, dims, strides,
+            box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Codes of one plane in 128-byte rows (see TmaMaps).  Returns 0 if the layout does not
+// fit, 1 for the wide form, 2 for the narrow form.
+int codes_map(CUtensorMap* m, const Plane& p, int row_bytes, int hpb, const DecodeArgs& a) {
+  if (p.cs[2] != row_bytes) return 0;  // the heads of a token must be contiguous
+  const int64_t token_bytes = static_cast<int64_t>(a.n_kv_heads) * row_bytes;
+  const int seg = hpb * row_bytes;  // the CTA's share of a token row
+  if (seg >= 128) {
+    if (seg % 128 || token_bytes % 128 || p.cs[1] < token_bytes || p.cs[0] < p.cs[1]) return 0;
+    const cuuint64_t dims[4] = {128, static_cast<cuuint64_t>(token_bytes / 128),
+                                static_cast<cuuint64_t>(a.block_size),
+                                static_cast<cuuint64_t>(a.num_blocks)};
+    const cuuint64_t strides[3] = {128, static_cast<cuuint64_t>(p.cs[1]),
+                                   static_cast<cuuint64_t>(p.cs[0])};
+    const cuuint32_t box[4] = {128, 1, 16, 1};
+    return encode(m, p.codes, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B) ? 1 : 0;
+  }
+  // narrow: the CTA holds every head and consecutive tokens are adjacent in memory
+  if (hpb != a.n_kv_heads || p.cs[1] != seg) return 0;
+  const int64_t page_bytes = static_cast<int64_t>(a.block_size) * seg;
+  if (page_bytes % 128 || p.cs[0] < page_bytes) return 0;
+  if ((16 * seg) % 1024) return 0;  // a tile must start on the swizzle's 1 KB period
+  const cuuint64_t dims[3] = {128, static_cast<cuuint64_t>(page_bytes / 128),
+                              static_cast<cuuint64_t>(a.num_blocks)};
+  const cuuint64_t strides[2] = {128, static_cast<cuuint64_t>(p.cs[0])};
+  const cuuint32_t box[3] = {128, static_cast<cuuint32_t>(16 * seg / 128), 1};
+  return encode(m, p.codes, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B) ? 2 : 0;
+}
+
+// One scale / zero array as bytes.  merged = false: (all heads of a token, tokens of a
+// page, blocks), box = the CTA's heads x 16 tokens.  merged = true (the CTA holds every
+// head and the rows of consecutive tokens are adjacent): (4-byte words of a page, 1,
+// blocks), box = the words of 16 tokens in one run.
+bool scale_map(CUtensorMap* m, __half* base, const int64_t st[3], int sb, int hpb, bool merged,
+               const DecodeArgs& a) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint32_t ones[3] = {1, 1, 1};
+  if (merged) {
+    const cuuint64_t dims[3] = {static_cast<cuuint64_t>(a.block_size) * hpb * sb / 4, 1,
+                                static_cast<cuuint64_t>(a.num_blocks)};
+    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(st[0]) * 2,
+                                   static_cast<cuuint64_t>(st[0]) * 2};
+    const cuuint32_t box[3] = {static_cast<cuuint32_t>(16 * hpb * sb / 4), 1, 1};
+    return fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, base, dims, strides, box, ones,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) ==
+           CUDA_SUCCESS;
+  }
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(a.n_kv_heads) * sb,
+                              static_cast<cuuint64_t>(a.block_size),
+                              static_cast<cuuint64_t>(a.num_blocks)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(st[1]) * 2,
+                                 static_cast<cuuint64_t>(st[0]) * 2};
+  const cuuint32_t box[3] = {static_cast<cuuint32_t>(hpb * sb), 16, 1};
+  return encode(m, base, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+}
+
+// Which scale layout the TMA path can take: 0 none, 1 per-token rows, 2 merged.
+int scale_layout(const int64_t st[3], const void* base, int ng, int sb, int hpb,
+                 const DecodeArgs& a) {
+  if (reinterpret_cast<uintptr_t>(base) % 16 || st[2] != ng) return 0;
+  if (hpb == a.n_kv_heads && st[1] == static_cast<int64_t>(hpb) * ng && (st[0] * 2) % 16 == 0 &&
+      st[0] >= static_cast<int64_t>(a.block_size) * hpb * ng && 16 * hpb * sb <= 1024)
+    return 2;
+  if ((hpb * sb) % 16 == 0 && (st[1] * 2) % 16 == 0 && (st[0] * 2) % 16 == 0 &&
+      st[1] >= static_cast<int64_t>(a.n_kv_heads) * ng && st[0] >= st[1])
+    return 1;
+  return 0;
+}
+
+// Tensor maps are cached by what determines them, so steady-state decode steps do
+// not call the driver.
+struct MapKey {
+  const void* ptrs[6];
+  int64_t strides[6][3];
+  int64_t num_blocks;
+  int n_kv_heads, head_dim, block_size, k_mode, v_mode, hpb;
+};
+
+bool build_maps(const DecodeArgs& a, int hpb, TmaMaps* out) {
+  if (a.block_size < 16) return false;
+  const int ng = a.head_dim / 32, sb = ng * 2;
+  // every TMA destination (a scale box is 16 tokens x hpb heads) must be 128-byte aligned
+  if ((16 * sb * hpb) % 128) return false;
+  const bool asym_k = a.k.mode == KNLP_KV_INT4_ASYM, asym_v = a.v.mode == KNLP_KV_INT4_ASYM;
+  const int lay = scale_layout(a.k.ss, a.k.scales, ng, sb, hpb, a);
+  if (lay == 0) return false;
+  if (scale_layout(a.v.ss, a.v.scales, ng, sb, hpb, a) != lay) return false;
+  if (asym_k && scale_layout(a.k.zs, a.k.zeros, ng, sb, hpb, a) != lay) return false;
+  if (asym_v && scale_layout(a.v.zs, a.v.zeros, ng, sb, hpb, a) != lay) return false;
+
+  MapKey key;
+  std::memset(&key, 0, sizeof(key));
+  const void* ptrs[6] = {a.k.codes, a.v.codes, a.k.scales, a.k.zeros, a.v.scales, a.v.zeros};
+  const int64_t* sts[6] = {a.k.cs, a.v.cs, a.k.ss, a.k.zs, a.v.ss, a.v.zs};
+  for (int i = 0; i < 6; ++i) {
+    key.ptrs[i] = ptrs[i];
+    for (int j = 0; j < 3; ++j) key.strides[i][j] = sts[i][j];
+  }
+  key.num_blocks = a.num_blocks;
+  key.n_kv_heads = a.n_kv_heads;
+  key.head_dim = a.head_dim;
+  key.block_size = a.block_size;
+  key.k_mode = a.k.mode;
+  key.v_mode = a.v.mode;
+  key.hpb = hpb;
+
+  static std::mutex mu;
+  static std::vector<std::pair<MapKey, TmaMaps>> cache;
+  std::lock_guard<std::mutex> lock(mu);
+  for (const auto& e : cache) {
+    if (std::memcmp(&e.first, &key, sizeof(key)) == 0) {
+      *out = e.second;
+      return true;
+    }
+  }
+  TmaMaps m;
+  std::memset(&m, 0, sizeof(m));
+  const bool merged = lay == 2;
+  m.scale_merged = merged ? 1 : 0;
+  const int kb = a.k.mode == KNLP_KV_INT8_G32 ? a.head_dim : a.head_dim / 2;
+  const int kform = codes_map(&m.k, a.k, kb, hpb, a);
+  const int vform = codes_map(&m.v, a.v, a.head_dim / 2, hpb, a);
+  if (kform == 0 || vform == 0) return false;
+  m.k_narrow = kform == 2;
+  m.v_narrow = vform == 2;
+  if (!scale_map(&m.ks, a.k.scales, a.k.ss, sb, hpb, merged, a)) return false;
+  if (!scale_map(&m.vs, a.v.scales, a.v.ss, sb, hpb, merged, a)) return false;
+  m.kz = m.ks;
+  m.vz = m.vs;
+  if (asym_k && !scale_map(&m.kz, a.k.zeros, a.k.zs, sb, hpb, merged, a)) return false;
+  if (asym_v && !scale_map(&m.vz, a.v.zeros, a.v.zs, sb, hpb, merged, a)) return false;
+  if (cache.size() >= 64) cache.erase(cache.begin());
+  cache.emplace_back(key, m);
+  *out = m;
+  return true;
+}
+
+template <int HD, int KMODE, int VMODE, bool SPLIT, bool TMA>
+int launch_inst(const DecodeArgs& a, const MmaParams& mp, const TmaMaps& tm, cudaStream_t st) {
+  using G = Geo<HD, KMODE, TMA ? 0 : 16>;
+  constexpr int kSmem = G::kSmemBytes + 1024;  // slack for the 1 KB alignment of the stages
+  auto kern = decode_mma_kernel<HD, KMODE, VMODE, SPLIT, TMA>;
   static int configured_dev = -1;  // per instantiation; the attribute is per device function
   int dev = 0;
   cudaGetDevice(&dev);
   if (configured_dev != dev) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             G::kSmemBytes) != cudaSuccess) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) !=
+        cudaSuccess) {
       cudaGetLastError();
       return KNLP_ERR_NO_DEVICE;
     }
@@ -768,65 +1402,95 @@ int launch_inst(const DecodeArgs& a, const MmaParams& mp, cudaStream_t st) {
   }
   const int hpb = 1 << mp.hpb_log2;
   dim3 grid(a.n_splits, a.n_kv_heads / hpb, a.n_seqs);
-  kern<<<grid, kThreads, G::kSmemBytes, st>>>(a, mp);
+  kern<<<grid, kThreads, kSmem, st>>>(a, mp, tm);
   return cudaGetLastError() == cudaSuccess ? KNLP_OK : KNLP_ERR_LAUNCH;
 }
 
 template <int HD, int KMODE, int VMODE>
-int launch_split(const DecodeArgs& a, const MmaParams& mp, bool split, cudaStream_t st) {
-  return split ? launch_inst<HD, KMODE, VMODE, true>(a, mp, st)
-               : launch_inst<HD, KMODE, VMODE, false>(a, mp, st);
+int launch_split(const DecodeArgs& a, const MmaParams& mp, bool split, const TmaMaps* tm,
+                 cudaStream_t st) {
+  static const TmaMaps none{};
+  if (tm) {
+    return split ? launch_inst<HD, KMODE, VMODE, true, true>(a, mp, *tm, st)
+                 : launch_inst<HD, KMODE, VMODE, false, true>(a, mp, *tm, st);
+  }
+  return split ? launch_inst<HD, KMODE, VMODE, true, false>(a, mp, none, st)
+               : launch_inst<HD, KMODE, VMODE, false, false>(a, mp, none, st);
 }
 
 template <int HD>
-int launch_modes(const DecodeArgs& a, const MmaParams& mp, bool split, cudaStream_t st) {
+int launch_modes(const DecodeArgs& a, const MmaParams& mp, bool split, const TmaMaps* tm,
+                 cudaStream_t st) {
   const int km = a.k.mode, vm = a.v.mode;
   if (km == KNLP_KV_INT4_ASYM && vm == KNLP_KV_INT4_ASYM)
-    return launch_split<HD, KNLP_KV_INT4_ASYM, KNLP_KV_INT4_ASYM>(a, mp, split, st);
+    return launch_split<HD, KNLP_KV_INT4_ASYM, KNLP_KV_INT4_ASYM>(a, mp, split, tm, st);
   if (km == KNLP_KV_INT4_SYM && vm == KNLP_KV_INT4_SYM)
-    return launch_split<HD, KNLP_KV_INT4_SYM, KNLP_KV_INT4_SYM>(a, mp, split, st);
+    return launch_split<HD, KNLP_KV_INT4_SYM, KNLP_KV_INT4_SYM>(a, mp, split, tm, st);
   if (km == KNLP_KV_INT8_G32 && vm == KNLP_KV_INT4_ASYM)
-    return launch_split<HD, KNLP_KV_INT8_G32, KNLP_KV_INT4_ASYM>(a, mp, split, st);
+    return launch_split<HD, KNLP_KV_INT8_G32, KNLP_KV_INT4_ASYM>(a, mp, split, tm, st);
   if (km == KNLP_KV_INT8_G32 && vm == KNLP_KV_INT4_SYM)
-    return launch_split<HD, KNLP_KV_INT8_G32, KNLP_KV_INT4_SYM>(a, mp, split, st);
+    return launch_split<HD, KNLP_KV_INT8_G32, KNLP_KV_INT4_SYM>(a, mp, split, tm, st);
   return 1;  // other combinations go to the generic kernel
 }
 
 bool aligned(const void* p, uintptr_t n) { return reinterpret_cast<uintptr_t>(p) % n == 0; }
 
-// The copy loop addresses with 32-bit strides and 16-byte pieces.
-bool plane_ok(const Plane& p, int head_dim) {
-  const int sb = head_dim / 32;  // fp16 elements per scale row
+// What the cp.async loader needs: 32-bit strides, 16-byte aligned pieces, the heads of
+// a token adjacent in memory (codes and scales), and scale rows that can be cut into
+// 16-byte pieces (a token's row of the CTA's heads is a multiple of 16 bytes, or the CTA
+// holds every head and consecutive tokens are adjacent).
+bool scale_array_ok(const __half* base, const int64_t st[3], int ng, int hpb, int n_kv_heads) {
+  constexpr int64_t kMax = 0x3fffffff;
+  if (!aligned(base, 16) || st[2] != ng) return false;
+  for (int i = 0; i < 2; ++i)
+    if (st[i] < 0 || st[i] > kMax || (st[i] * 2) % 16 != 0 && i == 0) return false;
+  const int tb = hpb * ng * 2;  // bytes of one token's row
+  if (tb % 16 == 0) return (st[1] * 2) % 16 == 0;
+  return hpb == n_kv_heads && st[1] * 2 == tb && 16 % tb == 0;
+}
+
+bool plane_ok(const Plane& p, int head_dim, int row_bytes, int hpb, int n_kv_heads) {
   constexpr int64_t kMax = 0x7fffffff;
-  if (!aligned(p.codes, 16)) return false;
-  for (int i = 0; i < 3; ++i) {
+  if (!aligned(p.codes, 16) || p.cs[2] != row_bytes) return false;
+  for (int i = 0; i < 2; ++i)
     if (p.cs[i] % 16 || p.cs[i] < 0 || p.cs[i] > kMax) return false;
-    if (p.ss[i] % sb || p.ss[i] < 0 || p.ss[i] > kMax) return false;
-    if (p.zeros && (p.zs[i] % sb || p.zs[i] < 0 || p.zs[i] > kMax)) return false;
-  }
-  if (!aligned(p.scales, sb * 2)) return false;
-  if (p.zeros && !aligned(p.zeros, sb * 2)) return false;
+  const int ng = head_dim / 32;
+  if (!scale_array_ok(p.scales, p.ss, ng, hpb, n_kv_heads)) return false;
+  if (p.zeros && !scale_array_ok(p.zeros, p.zs, ng, hpb, n_kv_heads)) return false;
   return true;
 }
 
 }  // namespace
 
-int launch_decode_mma(const DecodeArgs& a, cudaStream_t st) {
+int launch_decode_mma(const DecodeArgs& a, bool allow_tma, cudaStream_t st) {
   if (a.head_dim != 64 && a.head_dim != 128) return 1;
   if (a.n_q_heads % a.n_kv_heads) return 1;
   const int n_rep = a.n_q_heads / a.n_kv_heads;
   if (n_rep > 8) return 1;
   if (a.block_size & (a.block_size - 1)) return 1;  // pages must be a power of two
   if (a.num_blocks > 0x7fffffff) return 1;
-  if (!plane_ok(a.k, a.head_dim) || !plane_ok(a.v, a.head_dim)) return 1;
   MmaParams mp{};
   mp.hpb_log2 = 3;
   while (mp.hpb_log2 > 0 && (a.n_kv_heads % (1 << mp.hpb_log2))) --mp.hpb_log2;
+  const int hpb = 1 << mp.hpb_log2;
+  const int kb = a.k.mode == KNLP_KV_INT8_G32 ? a.head_dim : a.head_dim / 2;
+  if (!plane_ok(a.k, a.head_dim, kb, hpb, a.n_kv_heads) ||
+      !plane_ok(a.v, a.head_dim, a.head_dim / 2, hpb, a.n_kv_heads))
+    return 1;
   mp.page_log2 = 0;
   while ((1 << mp.page_log2) < a.block_size) ++mp.page_log2;
   const bool split = n_rep <= 4;
-  return a.head_dim == 128 ? launch_modes<128>(a, mp, split, st)
-                           : launch_modes<64>(a, mp, split, st);
+  TmaMaps tm;
+#ifdef KNLP_EXP_NOTMA
+  allow_tma = false;
+#endif
+#ifdef KNLP_EXP_FORCETMA
+  allow_tma = true;
+#endif
+  const bool use_tma = allow_tma && build_maps(a, hpb, &tm);
+  const TmaMaps* tmp = use_tma ? &tm : nullptr;
+  return a.head_dim == 128 ? launch_modes<128>(a, mp, split, tmp, st)
+                           : launch_modes<64>(a, mp, split, tmp, st);
 }
 
 }  // namespace knlp

@@ -199,6 +199,22 @@ def plan_splits(num_seqs: int, num_heads: int, num_kv_heads: int, head_size: int
     return n.value
 
 
+def _decode_flags(force_generic) -> int:
+    """``force_generic``: False = best kernel for the layout (tensor-core kernel staged
+    with cp.async, else the generic one); "tma" = tensor-core kernel staged with TMA
+    tensor copies and mbarriers (measured slower for this access pattern; kept
+    selectable); True = stride-generic CUDA-core kernel."""
+    if force_generic == "tma":
+        return _lib.DECODE_USE_TMA
+    return _lib.DECODE_FORCE_GENERIC if force_generic else 0
+
+
+def device_status() -> int:
+    """Synchronise and return (then clear) the decode kernels' device status word:
+    0 = clean, 1 = a bounded barrier wait ran out inside a kernel."""
+    return _lib.load().knlp_b200_debug_status()
+
+
 def decode_partials(
     query: torch.Tensor, k_plane: _lib.KvPlane, v_plane: _lib.KvPlane, num_blocks: int,
     block_table: torch.Tensor, seq_lens: torch.Tensor, num_kv_heads: int, head_size: int,
@@ -231,7 +247,7 @@ def decode_partials(
             block_table.data_ptr(), block_table.stride(0), seq_lens.data_ptr(), num_blocks,
             S, Hq, num_kv_heads, head_size, block_size, n_splits, max_seq_len,
             pm.data_ptr(), pl.data_ptr(), po.data_ptr(),
-            _lib.DECODE_FORCE_GENERIC if force_generic else 0, _stream(dev))
+            _decode_flags(force_generic), _stream(dev))
     _lib.check(rc, "knlp_b200_decode_splitk")
     return pm, pl, po
 

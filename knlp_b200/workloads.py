@@ -190,10 +190,13 @@ def config(name: str, device, *, seed: Optional[int] = None, scale: float = 1.0,
         return build(name, n_seqs=1, n_q_heads=12, n_kv_heads=12, head_dim=64, seq_lens=[ctx(1024)],
                      seed=1000 if seed is None else seed, device=device, kv_dtype=torch.float32,
                      q_dtype=torch.float32, head_slice=head_slice, extra_blocks_per_seq=extra_blocks_per_seq)
-    if name in ("llama8b_b32_8k", "llama8b_b32_128k"):
-        T = 131072 if name.endswith("128k") else 8192
-        return build(name, n_seqs=32, n_q_heads=32, n_kv_heads=8, head_dim=128,
-                     seq_lens=[ctx(T)] * 32, seed=2000 if seed is None else seed, device=device,
+    import re
+    m = re.fullmatch(r"llama8b_b(\d+)_(\d+)k", name)
+    if m and name != "llama8b_b1_384k":
+        # llama8b_b<batch>_<context in Ki tokens>k: uniform batch of the Llama-3-8B shape
+        B, T = int(m.group(1)), int(m.group(2)) * 1024
+        return build(name, n_seqs=B, n_q_heads=32, n_kv_heads=8, head_dim=128,
+                     seq_lens=[ctx(T)] * B, seed=2000 if seed is None else seed, device=device,
                      head_slice=head_slice, extra_blocks_per_seq=extra_blocks_per_seq)
     if name == "llama8b_b1_384k":
         return build(name, n_seqs=1, n_q_heads=32, n_kv_heads=8, head_dim=128,

@@ -209,7 +209,7 @@ def _golden_decode_setup(G, mode, dev):
 
 @pytest.mark.parametrize("case", DECODE_CASES)
 @pytest.mark.parametrize("mode", ["asym", "sym", "k8v4"])
-@pytest.mark.parametrize("generic", [False, True])
+@pytest.mark.parametrize("generic", [False, "tma", True])
 def test_decode_golden(case, mode, generic, cuda_device):
     G = load_golden(case)
     run, oracle = _golden_decode_setup(G, mode, cuda_device)
@@ -253,7 +253,7 @@ def test_config1_gpt2_mha_exact_shape(cuda_device):
     from knlp_b200 import workloads
     w = workloads.config("gpt2_mha_1k", cuda_device)
     ref = _workload_oracle(w)
-    for generic in (False, True):
+    for generic in (False, "tma", True):
         out = w.decode(out_dtype=torch.float32, force_generic=generic)
         assert_close(out.cpu().numpy(), ref, f"gpt2 generic={generic}")
 
@@ -271,6 +271,8 @@ def test_configs_scaled_full_compare(name, scale, cuda_device):
     assert_close(out1.cpu().numpy(), ref, name + "/1 split")
     outg = w.decode(out_dtype=torch.float32, force_generic=True)
     assert_close(outg.cpu().numpy(), ref, name + "/generic")
+    outc = w.decode(out_dtype=torch.float32, force_generic="tma")
+    assert_close(outc.cpu().numpy(), ref, name + "/TMA staging")
     # determinism: same launch twice gives identical bits
     assert torch.equal(out, w.decode(out_dtype=torch.float32))
 
@@ -283,7 +285,7 @@ def test_decode_edge_lengths(length, cuda_device):
                         seed=77 + length, device=cuda_device, shuffle_pages=True,
                         extra_blocks_per_seq=1)
     ref = _workload_oracle(w)
-    for kw in (dict(), dict(n_splits=4), dict(force_generic=True)):
+    for kw in (dict(), dict(n_splits=4), dict(force_generic="tma"), dict(force_generic=True)):
         out = w.decode(out_dtype=torch.float32, **kw).cpu().numpy()
         assert_close(out, ref, f"len={length} {kw}")
         if length == 0:
@@ -342,6 +344,12 @@ def test_combine_vs_oracle(cuda_device):
     out3 = ops.combine_partials(torch.stack([m, m2]), torch.stack([l, l2]), torch.stack([o, o2]),
                                 parts_dim=0)
     np.testing.assert_allclose(out3.cpu().numpy(), ref, atol=1e-5, rtol=1e-5)
+
+
+def test_zz_device_status_is_clean(cuda_device):
+    """No kernel of this session gave up on a barrier wait."""
+    from knlp_b200 import ops
+    assert ops.device_status() == 0
 
 
 def test_cpu_tensor_is_refused():
