@@ -199,15 +199,19 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    from knlp_b200 import shard as shardlib
+    ctx_mode = args.shard == "context" and world > 1
     total_kv_heads = 8
-    if total_kv_heads % world:
-        raise SystemExit("--gpus must divide the 8 kv heads")
-    per = total_kv_heads // world
-    hs = slice(rank * per, (rank + 1) * per) if world > 1 else None
+    hs = None
+    if world > 1 and not ctx_mode:
+        if total_kv_heads % world:
+            raise SystemExit("--gpus must divide the 8 kv heads")
+        hs = shardlib.head_shard(total_kv_heads, world, rank)
 
     # one spare page per sequence so the end-to-end leg can append a token
     w = workloads.config(args.workload, dev, scale=args.scale, head_slice=hs,
-                         extra_blocks_per_seq=1)
+                         extra_blocks_per_seq=1,
+                         ctx_shard=(world, rank) if ctx_mode else None)
     S, Hq, d = w.query.shape
     n_splits = args.splits or ops.plan_splits(S, Hq, w.n_kv_heads, d, PAGE, w.max_seq_len)
     from knlp_b200.ops import _plane, _int4_mode, _lib
@@ -228,6 +232,9 @@ def run_ours(args):
                                          n_splits=n_splits)
         if rec is not None:
             rec[1].record()
+        if ctx_mode:
+            # context shard: one packed partial per rank, ONE NCCL all-gather, final merge
+            return shardlib.context_sharded_decode((pm, pl, po), out_dtype=w.query.dtype)
         return ops.combine_partials(pm, pl, po, out_dtype=w.query.dtype)
 
     for _ in range(max(args.warmup, 3)):
@@ -291,7 +298,10 @@ def run_ours(args):
         workloads.append_tokens(caches, kn, vn, sl, w.k_mode, w.v_mode)
         pm, pl, po = ops.decode_partials(q, kp, vp, nblocks, bt, ln, w.n_kv_heads, d, PAGE,
                                          max_seq_len=w.max_seq_len + 1, n_splits=n_splits)
-        o = ops.combine_partials(pm, pl, po, out_dtype=w.query.dtype)
+        if ctx_mode:
+            o = shardlib.context_sharded_decode((pm, pl, po), out_dtype=w.query.dtype)
+        else:
+            o = ops.combine_partials(pm, pl, po, out_dtype=w.query.dtype)
         out_h.copy_(o, non_blocking=True)
 
     for _ in range(3):
@@ -332,7 +342,9 @@ def run_ours(args):
                        "q_heads_per_gpu": Hq, "kv_heads_per_gpu": w.n_kv_heads, "head_dim": d,
                        "context": w.max_seq_len, "kv": f"K {w.k_mode} / V {w.v_mode}, group 32",
                        "page": PAGE, "n_splits": n_splits,
-                       "parallelism": f"kv-head shard x{world}" if world > 1 else "single GPU",
+                       "parallelism": (f"context shard x{world} (+1 NCCL all-gather of partials)"
+                                       if ctx_mode else f"kv-head shard x{world}")
+                       if world > 1 else "single GPU",
                        "l2": "inputs larger than L2 (no flush needed)"
                              if alg_local > 4 * 126e6 else "inputs NOT larger than L2",
                        "algorithmic_bytes_per_step": alg_total},
@@ -344,7 +356,7 @@ def run_ours(args):
             "e2e": {"value": alg_total / (e2e_ms / K / 1e3) / 1e12, "unit": UNIT,
                     "ms_per_step": e2e_ms / K, "h2d_bytes_per_step": int(h2d_total),
                     "d2h_bytes_per_step": int(d2h_total)},
-            "gpu_launches": 2 * K,
+            "gpu_launches": (3 if ctx_mode else 2) * K,
         }
         if world == 1 and not args.no_cpu:
             nbytes, secs, threads, desc = cpu_reference_sample(args.workload, args.scale, 32768, 4)
@@ -367,6 +379,8 @@ def main():
     ap.add_argument("--scale", type=float, default=1.0)
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--shard", default="heads", choices=["heads", "context"],
+                    help="how N > 1 GPUs split the work (default: kv heads, no exchange)")
     ap.add_argument("--profile", action="store_true",
                     help="short run for use under ncu: timed steps only, one JSON line of timings")
     args = ap.parse_args()

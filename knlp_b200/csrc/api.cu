@@ -117,17 +117,22 @@ int knlp_b200_decode_plan(int n_seqs, int n_q_heads, int n_kv_heads, int head_di
   const int64_t base = static_cast<int64_t>(n_seqs) * (n_kv_heads / hpb);
   const int64_t slots = 2LL * sm_count();
   const int max_splits = max_seq_len >= 512 ? (max_seq_len / 256 > 1024 ? 1024 : max_seq_len / 256) : 1;
+  // Cost model (microseconds, coarse, measured on B200): a wave of CTAs costs a fixed
+  // set-up plus 1.4 us per 16-token x 8-head stage of its split; merging costs a
+  // little per split.  Fewer, longer splits amortise the set-up; more splits fill the
+  // machine and even out ragged batches.
+  const int tokens_per_stage = 16 * (8 / hpb);
   int best = 1;
-  double best_score = -1.0;
+  double best_cost = 1e30;
   for (int n = 1; n <= max_splits; ++n) {
     const int64_t ctas = base * n;
     const int64_t waves = (ctas + slots - 1) / slots;
-    if (waves > 6 && n > 1) break;
-    const double eff = static_cast<double>(ctas) / static_cast<double>(waves * slots);
-    // more waves smooth out uneven sequence lengths; weight them mildly
-    const double score = eff * (1.0 - 0.08 / static_cast<double>(waves));
-    if (score > best_score + 1e-9) {
-      best_score = score;
+    if (waves > 8 && n > 1) break;
+    const int chunk = split_chunk(max_seq_len, n);
+    const double stages = static_cast<double>((chunk + tokens_per_stage - 1) / tokens_per_stage);
+    const double cost = static_cast<double>(waves) * (6.0 + 1.4 * stages) + 0.03 * n + 3.0;
+    if (cost < best_cost - 1e-9) {
+      best_cost = cost;
       best = n;
     }
   }

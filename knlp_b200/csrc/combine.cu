@@ -4,7 +4,10 @@
 // online-softmax recurrence of its decode loop
 // (fused-quant/fused_int4.v0.1.0.py:808-815, 883-887) applied across parts:
 //   m = max_i m_i,  l = sum_i l_i e^(m_i - m),  o = sum_i o_i e^(m_i - m) [/ l]
-// One CTA per (sequence, q head) row; a thread owns head_dim/blockDim elements.
+// One CTA of 8 warps per (sequence, q head) row.  The parts are dealt to the warps
+// round-robin and every lane owns head_dim/32 consecutive elements, so a warp reads
+// one part's o row as one contiguous run and the loads of different parts are
+// independent (several in flight per warp).  The warps' sums meet in shared memory.
 // Parts with l == 0 (empty splits) are skipped; a row with no tokens gives 0.
 
 #include "common.cuh"
@@ -12,7 +15,9 @@
 namespace knlp {
 namespace {
 
-constexpr int kThreads = 128;
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+constexpr int kMaxEpl = 8;  // head_dim <= 256
 
 __global__ void __launch_bounds__(kThreads)
 combine_kernel(const float* __restrict__ pm, const float* __restrict__ pl,
@@ -20,32 +25,65 @@ combine_kernel(const float* __restrict__ pm, const float* __restrict__ pl,
                int64_t o_row, int64_t o_part, void* out, int out_dtype, int64_t out_row,
                float* out_m, float* out_l, int64_t out_ml, int head_dim) {
   const int64_t row = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const float* rm = pm + row * ml_row;
   const float* rl = pl + row * ml_row;
   const float* ro = po + row * o_row;
+  const int epl = head_dim >> 5;  // elements per lane (head_dim is a multiple of 32)
 
+  __shared__ float s_red[kWarps];
+  __shared__ float s_l[kWarps];
+  __shared__ float s_o[kWarps][32 * kMaxEpl];
+
+  // global maximum over the non-empty parts
   float m = -INFINITY;
-  for (int p = 0; p < n_parts; ++p) {
+  for (int p = threadIdx.x; p < n_parts; p += kThreads) {
     if (rl[p * ml_part] > 0.0f) m = fmaxf(m, rm[p * ml_part]);
   }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if (lane == 0) s_red[warp] = m;
+  __syncthreads();
+  m = s_red[0];
+#pragma unroll
+  for (int w = 1; w < kWarps; ++w) m = fmaxf(m, s_red[w]);
+
+  // this warp's share of the parts
+  float l = 0.0f;
+  float acc[kMaxEpl];
+#pragma unroll
+  for (int i = 0; i < kMaxEpl; ++i) acc[i] = 0.0f;
+#pragma unroll 4
+  for (int p = warp; p < n_parts; p += kWarps) {
+    const float lp = rl[p * ml_part];
+    const float w = lp > 0.0f ? __expf(rm[p * ml_part] - m) : 0.0f;
+    l += lp * w;
+    const float* src = ro + p * o_part + lane * epl;
+#pragma unroll
+    for (int i = 0; i < kMaxEpl; ++i)
+      if (i < epl) acc[i] = fmaf(w > 0.0f ? src[i] : 0.0f, w, acc[i]);
+  }
+  if (lane == 0) s_l[warp] = l;
+#pragma unroll
+  for (int i = 0; i < kMaxEpl; ++i)
+    if (i < epl) s_o[warp][lane * epl + i] = acc[i];
+  __syncthreads();
+
   for (int e = threadIdx.x; e < head_dim; e += kThreads) {
-    float l = 0.0f, o = 0.0f;
-    for (int p = 0; p < n_parts; ++p) {
-      const float lp = rl[p * ml_part];
-      if (lp > 0.0f) {
-        const float w = __expf(rm[p * ml_part] - m);
-        l += lp * w;
-        o += ro[p * o_part + e] * w;
-      }
+    float lt = 0.0f, ot = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      lt += s_l[w];
+      ot += s_o[w][e];
     }
     if (out_m != nullptr) {
-      static_cast<float*>(out)[row * out_row + e] = o;
+      static_cast<float*>(out)[row * out_row + e] = ot;
       if (e == 0) {
         out_m[row * out_ml] = m;
-        out_l[row * out_ml] = l;
+        out_l[row * out_ml] = lt;
       }
     } else {
-      store_elem_rt(out, row * out_row + e, l > 0.0f ? o / l : 0.0f, out_dtype);
+      store_elem_rt(out, row * out_row + e, lt > 0.0f ? ot / lt : 0.0f, out_dtype);
     }
   }
 }
@@ -57,8 +95,10 @@ int launch_combine(const float* pm, const float* pl, const float* po, int n_part
                    int out_dtype, int64_t out_row, float* out_m, float* out_l, int64_t out_ml,
                    int n_rows, int head_dim, cudaStream_t st) {
   if (n_rows == 0) return KNLP_OK;
+  if (head_dim % 32 || head_dim > 32 * kMaxEpl) return KNLP_ERR_SHAPE;
   combine_kernel<<<n_rows, kThreads, 0, st>>>(pm, pl, po, n_parts, ml_row, ml_part, o_row, o_part,
-                                              out, out_dtype, out_row, out_m, out_l, out_ml, head_dim);
+                                              out, out_dtype, out_row, out_m, out_l, out_ml,
+                                              head_dim);
   return cudaGetLastError() == cudaSuccess ? KNLP_OK : KNLP_ERR_LAUNCH;
 }
 

@@ -79,20 +79,6 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
 }
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
-#if defined(KNLP_EXP_L2ONLY)
-  if (src_bytes) asm volatile("prefetch.global.L2 [%0];\n" ::"l"(src) : "memory");
-  return;
-#elif defined(KNLP_EXP_REGONLY)
-  if (src_bytes) {
-    uint32_t x, y, z, w;
-    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(x), "=r"(y), "=r"(z), "=r"(w)
-                 : "l"(src)
-                 : "memory");
-    asm volatile("" ::"r"(x), "r"(y), "r"(z), "r"(w));
-  }
-  return;
-#endif
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src),
                "r"(src_bytes)
                : "memory");
@@ -161,11 +147,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   asm volatile(
       "{\n"
       ".reg .pred p;\n"
-#ifdef KNLP_EXP_TESTWAIT
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-#else
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-#endif
       "selp.u32 %0, 1, 0, p;\n"
       "}\n"
       : "=r"(ok)
@@ -301,9 +283,6 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
   constexpr bool kAsymK = (KMODE == KNLP_KV_INT4_ASYM);
   constexpr bool kAsymV = (VMODE == KNLP_KV_INT4_ASYM);
 
-#ifdef KNLP_EXP_TIMELINE
-  const long long tl_start = clock64();
-#endif
   extern __shared__ uint8_t smem_raw[];
   // swizzled TMA tiles need their natural alignment: round the base up to 1 KB
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -489,120 +468,47 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
     return static_cast<uint32_t>(raw < 0 ? 0 : (raw > max_blk ? max_blk : raw));
   };
 
-#ifdef KNLP_EXP_TIMELINE
-  long long tl_cp = 0, tl_first = 0, tl_addr = 0, tl_is0 = 0, tl_pg = 0;
-#endif
-  constexpr int kPiecesAll = kKPer + kVPer + 1;
-  uint4 st_regs[kPiecesAll];
-  uint32_t st_dsts[kPiecesAll];
-  bool st_pending = false;
-  auto flush_pending = [&]() {
-    if (st_pending) {
-#pragma unroll
-      for (int n = 0; n < kPiecesAll; ++n) {
-#ifdef KNLP_EXP_NOSTS
-        // consume the loaded registers with a real instruction, but write nothing
-        if ((st_regs[n].x ^ st_regs[n].y ^ st_regs[n].z ^ st_regs[n].w) == 0x9e3779b9u &&
-            st_dsts[n] == 1u)
-          a.part_l[0] = 1.0f;
-        continue;
-#endif
-        if (n < kPiecesAll - 1 || s_on)
-          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(st_dsts[n]),
-                       "r"(st_regs[n].x), "r"(st_regs[n].y), "r"(st_regs[n].z), "r"(st_regs[n].w)
-                       : "memory");
-      }
-      st_pending = false;
-    }
-  };
-  auto issue_stage = [&](int it) {
+  // The copies of a stage: part 0 = K codes, 1 = V codes, 2 = scales and zeros.  They
+  // are all issued at the top of an iteration (spreading them over the iteration
+  // measured slower).
+  auto issue_part = [&](int it, int part) {
     const int stage_tok0 = start + it * TT;
     const int page0 = stage_tok0 >> mp.page_log2;
     const int slot = it % (kStages + 1);
-#ifdef KNLP_EXP_READSLOT0
-    const uint32_t stage_off = static_cast<uint32_t>(it % kStages == 0 ? 1 : it % kStages) * G::kStageBytes;
-#else
     const uint32_t stage_off = static_cast<uint32_t>(it % kStages) * G::kStageBytes;
-#endif
-    constexpr int kPieces = kKPer + kVPer + 1;
-    const uint8_t* srcs[kPieces];
-    uint32_t dsts[kPieces];
-    bool lives[kPieces];
+    if (part == 0) {
 #pragma unroll
-    for (int n = 0; n < kKPer; ++n) {
-      const int tok = stage_tok0 + k_tt0 + n * k_dtt;
-      lives[n] = tok < end;
-      const uint32_t blk = lives[n] ? page_id(slot, tok, page0) : 0u;
-      srcs[n] =
-          k_src0 + (static_cast<uint64_t>(blk) * kcs0 + static_cast<uint32_t>(tok & page_mask) * kcs1);
-      dsts[n] = k_dst[n] + stage_off;
-    }
+      for (int n = 0; n < kKPer; ++n) {
+        const int tok = stage_tok0 + k_tt0 + n * k_dtt;
+        const bool live = tok < end;
+        const uint32_t blk = live ? page_id(slot, tok, page0) : 0u;
+        const uint8_t* src = k_src0 + (static_cast<uint64_t>(blk) * kcs0 +
+                                       static_cast<uint32_t>(tok & page_mask) * kcs1);
+        cp_async16(k_dst[n] + stage_off, src, live ? 16 : 0);  // 0 -> zero fill
+      }
+    } else if (part == 1) {
 #pragma unroll
-    for (int n = 0; n < kVPer; ++n) {
-      const int tok = stage_tok0 + v_tt0 + n * v_dtt;
-      lives[kKPer + n] = tok < end;
-      const uint32_t blk = lives[kKPer + n] ? page_id(slot, tok, page0) : 0u;
-      srcs[kKPer + n] =
-          v_src0 + (static_cast<uint64_t>(blk) * vcs0 + static_cast<uint32_t>(tok & page_mask) * vcs1);
-      dsts[kKPer + n] = v_dst[n] + stage_off;
-    }
-    {
+      for (int n = 0; n < kVPer; ++n) {
+        const int tok = stage_tok0 + v_tt0 + n * v_dtt;
+        const bool live = tok < end;
+        const uint32_t blk = live ? page_id(slot, tok, page0) : 0u;
+        const uint8_t* src = v_src0 + (static_cast<uint64_t>(blk) * vcs0 +
+                                       static_cast<uint32_t>(tok & page_mask) * vcs1);
+        cp_async16(v_dst[n] + stage_off, src, live ? 16 : 0);
+      }
+    } else if (s_on) {
       const int tok = stage_tok0 + s_tt;
-      lives[kPieces - 1] = s_on && tok < end;
-      const uint32_t blk = lives[kPieces - 1] ? page_id(slot, tok, page0) : 0u;
-      srcs[kPieces - 1] =
-          s_src0 + (static_cast<uint64_t>(blk) * s_st0 + static_cast<uint32_t>(tok & page_mask) * s_st1);
-      dsts[kPieces - 1] = s_dst + stage_off;
+      const bool live = tok < end;
+      const uint32_t blk = live ? page_id(slot, tok, page0) : 0u;
+      const uint8_t* src = s_src0 + (static_cast<uint64_t>(blk) * s_st0 +
+                                     static_cast<uint32_t>(tok & page_mask) * s_st1);
+      cp_async16(s_dst + stage_off, src, live ? 16 : 0);
     }
-#if defined(KNLP_DEFER_COPY)
-#pragma unroll
-    for (int n = 0; n < kPieces; ++n) {
-      st_regs[n] = make_uint4(0u, 0u, 0u, 0u);
-      st_dsts[n] = dsts[n];
-      if (lives[n])
-        asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];\n"
-                     : "=r"(st_regs[n].x), "=r"(st_regs[n].y), "=r"(st_regs[n].z),
-                       "=r"(st_regs[n].w)
-                     : "l"(srcs[n]));
-    }
-    st_pending = true;
-#elif defined(KNLP_SYNC_COPY)
-    // global -> registers -> shared: the warp waits for its own loads (the other
-    // warps keep the SM busy meanwhile)
-    uint4 regs[kPieces];
-#pragma unroll
-    for (int n = 0; n < kPieces; ++n) {
-      regs[n] = make_uint4(0u, 0u, 0u, 0u);
-      if (lives[n])
-        asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];\n"
-                     : "=r"(regs[n].x), "=r"(regs[n].y), "=r"(regs[n].z), "=r"(regs[n].w)
-                     : "l"(srcs[n]));
-    }
-#pragma unroll
-    for (int n = 0; n < kPieces; ++n) {
-      if (n < kPieces - 1 || s_on)
-        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(dsts[n]), "r"(regs[n].x),
-                     "r"(regs[n].y), "r"(regs[n].z), "r"(regs[n].w)
-                     : "memory");
-    }
-#else
-#ifdef KNLP_EXP_TIMELINE
-#pragma unroll
-    for (int n = 0; n < kPieces; ++n) asm volatile("" ::"l"(srcs[n]), "r"(dsts[n]) : "memory");
-    const long long ta = clock64();
-    tl_addr += ta - tl_is0;
-#endif
-#pragma unroll
-    for (int n = 0; n < kPieces; ++n) {
-      if (n < kPieces - 1 || s_on) cp_async16(dsts[n], srcs[n], lives[n] ? 16 : 0);  // 0 -> zero fill
-#ifdef KNLP_EXP_TIMELINE
-      if (n == 0) tl_first += clock64() - ta;
-#endif
-    }
-#ifdef KNLP_EXP_TIMELINE
-    tl_cp += clock64() - ta;
-#endif
-#endif
+  };
+  auto issue_stage = [&](int it) {
+    issue_part(it, 0);
+    issue_part(it, 1);
+    issue_part(it, 2);
   };
 
   const int n_iters = (end - start + TT - 1) / TT;
@@ -670,21 +576,6 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
         const int col = cc % nbox;
         const void* map = is_v ? static_cast<const void*>(&tm.v) : static_cast<const void*>(&tm.k);
         const uint32_t region = stage_base + (is_v ? G::kOffV : G::kOffK);
-#ifdef KNLP_EXP_BULKROWS
-        if (seg == 512) {
-          const Plane& pl = is_v ? a.v : a.k;
-          for (int r = 0; r < 4; ++r) {
-            const int t = col * 4 + r;
-            const uint8_t* src = pl.codes + static_cast<int64_t>(blk) * pl.cs[0] +
-                                 static_cast<int64_t>(off + t) * pl.cs[1] + hb * seg;
-            asm volatile(
-                "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], "
-                "%2, [%3];\n" ::"r"(region + (tl * 16 + t) * 512),
-                "l"(src), "r"(512), "r"(full)
-                : "memory");
-          }
-        } else
-#endif
         if (seg >= 128) {
           tma_load_4d(region + ((tl * nbox + col) << 11), map, full, 0,
                       ((hb * seg) >> 7) + col, off, blk);
@@ -768,9 +659,6 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
 #pragma unroll
     for (int s = 0; s < kStages - 1; ++s) {
       if (s < n_iters) issue_stage(s);
-#ifdef KNLP_DEFER_COPY
-      flush_pending();
-#endif
       cp_async_commit();
     }
   }
@@ -807,10 +695,6 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
   const int sc_row0 = ((((w_tile << 4) + fr) << hpb_log2) + w_head) * G::SB;
   const int sc_row8 = (8 * G::SB) << hpb_log2;
 
-#ifdef KNLP_EXP_TIMELINE
-  long long tl_wait = 0, tl_bar = 0, tl_body = 0, tl_prev = 0, tl_issue = 0, tl_flush = 0;
-  const long long tl_loop0 = clock64();
-#endif
   for (int it = 0; it < n_iters; ++it) {
     if constexpr (TMA) {
       // the warps take turns refilling the slot that iteration it-1 released
@@ -829,58 +713,20 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
         break;
       }
     } else {
-#ifdef KNLP_EXP_TIMELINE
-      const long long tlf = clock64();
-#endif
-#ifdef KNLP_DEFER_COPY
-      flush_pending();
-#endif
-#ifdef KNLP_EXP_TIMELINE
-      const long long tl0 = clock64();
-      tl_flush += tl0 - tlf;
-#endif
-#ifndef KNLP_EXP_NOWAIT
       cp_async_wait<kStages - 2>();
-#endif
-#ifdef KNLP_EXP_TIMELINE
-      const long long tl1 = clock64();
-#endif
       __syncthreads();
-#ifdef KNLP_EXP_TIMELINE
-      const long long tl2 = clock64();
-      tl_wait += tl1 - tl0;
-      tl_bar += tl2 - tl1;
-      if (it > 0) tl_body += tl0 - tl_prev;
-      tl_prev = tl2;
-#endif
       if (tid < 16) {
         pg_tab[(it + kStages) % (kStages + 1)][tid] = pg_reg;  // loaded one iteration ago
         pg_reg = load_pages(it + kStages + 1);
       }
+    }
+    if constexpr (!TMA) {
       const int nx = it + kStages - 1;
-#ifdef KNLP_EXP_TIMELINE
-      asm volatile("" ::: "memory");
-      tl_is0 = clock64();
-      tl_pg += tl_is0 - tl2;
-#endif
-#ifdef KNLP_EXP_NOCOPY
-      if (false) {
-#else
-      if (nx < n_iters) {
-#endif
-        issue_stage(nx);
-      }
+      if (nx < n_iters) issue_stage(nx);
       cp_async_commit();
-#ifdef KNLP_EXP_TIMELINE
-      tl_issue += clock64() - tl2;
-#endif
     }
 
-#ifdef KNLP_EXP_READSLOT0
-    const uint32_t stage_off = 0;
-#else
     const uint32_t stage_off = static_cast<uint32_t>(it % kStages) * G::kStageBytes;
-#endif
     const uint8_t* st = smem + stage_off;
     const int tok0 = start + it * TT + w_tile * 16;  // first token of this warp's tile
     const uint32_t empty_bar = bar0 + (kStages + it % kStages) * 8;
@@ -890,13 +736,6 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
       }
       continue;
     }
-#ifdef KNLP_EXP_NOCOMPUTE
-    if (st[tid] == 255 && st[tid + 999] == 254) oacc[0][0][0] += 1.0f;
-    if constexpr (TMA) {
-      if (lane == 0) mbar_arrive(empty_bar);
-    }
-    continue;
-#endif
     // Rows past the end of a partial tile may hold whatever the page holds there (a TMA
     // box is always whole; a 16-byte scale piece can span two tokens), so their scales
     // are masked before use.
@@ -1027,7 +866,6 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
       }
     }
 
-#ifndef KNLP_EXP_NOPV
     // ---------------- P' = p * vscale per group, transposed into the B operand ----
     float vs[2][NG];
 #pragma unroll
@@ -1098,7 +936,6 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
         mma16816(oacc[g][1], e0[2], e0[3], e1[2], e1[3], pb[0], pb[1]);
       }
     }
-#endif
     if constexpr (TMA) {
       // this warp is done reading the stage: release its slot to the refilling warp
       __syncwarp();
@@ -1106,15 +943,6 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
     }
   }
 
-#ifdef KNLP_EXP_TIMELINE
-  if (lane == 0 && blockIdx.x == 5 && blockIdx.z == 3)
-    printf("prologue %lld  loop %lld cycles; per iter: page block %lld  addr %lld\n", tl_loop0 - tl_start,
-           clock64() - tl_loop0, tl_pg / n_iters, tl_addr / n_iters);
-  if (lane == 0 && blockIdx.x == 5 && blockIdx.z == 3)
-    printf("warp %d iters %d: wait %lld  barrier %lld  body(issue+compute) %lld  issue %lld  flush %lld  cp.async x5 %lld  first %lld cycles per iter\n",
-           warp, n_iters, tl_wait / n_iters, tl_bar / n_iters, tl_body / max(n_iters - 1, 1),
-           tl_issue / n_iters, tl_flush / n_iters, tl_cp / n_iters, tl_first / n_iters);
-#endif
   // ---------------- epilogue: reduce lanes, merge the warps of a head, write ----
   cp_async_wait<0>();
   __syncthreads();  // all stages consumed; shared memory is reused below
@@ -1481,12 +1309,6 @@ int launch_decode_mma(const DecodeArgs& a, bool allow_tma, cudaStream_t st) {
   while ((1 << mp.page_log2) < a.block_size) ++mp.page_log2;
   const bool split = n_rep <= 4;
   TmaMaps tm;
-#ifdef KNLP_EXP_NOTMA
-  allow_tma = false;
-#endif
-#ifdef KNLP_EXP_FORCETMA
-  allow_tma = true;
-#endif
   const bool use_tma = allow_tma && build_maps(a, hpb, &tm);
   const TmaMaps* tmp = use_tma ? &tm : nullptr;
   return a.head_dim == 128 ? launch_modes<128>(a, mp, split, tmp, st)

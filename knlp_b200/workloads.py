@@ -114,8 +114,12 @@ def build(name: str, *, n_seqs: int, n_q_heads: int, n_kv_heads: int, head_dim: 
           seq_lens, seed: int, device, kv_dtype=torch.bfloat16, q_dtype=torch.bfloat16,
           k_mode: str = "int4_asym", v_mode: str = "int4_asym", shuffle_pages: bool = False,
           head_slice: Optional[slice] = None, extra_blocks_per_seq: int = 0,
-          chunk_tokens: int = 32768) -> Workload:
+          chunk_tokens: int = 32768, ctx_shard: Optional[tuple] = None) -> Workload:
     """Build one workload on ``device``.
+
+    ``ctx_shard = (world, rank)`` keeps only the rank's contiguous, page-aligned token
+    segment of every sequence (``shard.context_shard``): the cache of one rank of a
+    context shard, holding exactly the values the unsharded cache holds there.
 
     ``head_slice`` keeps only those kv heads (and their q heads): the cache of one
     rank of a kv-head shard.  Values are drawn per (sequence, token chunk) from a
@@ -123,8 +127,14 @@ def build(name: str, *, n_seqs: int, n_q_heads: int, n_kv_heads: int, head_dim: 
     shard of a rank holds exactly the values the unsharded cache would.
     """
     cpu_gen = torch.Generator().manual_seed(seed)
-    lens = [int(x) for x in seq_lens]
-    assert len(lens) == n_seqs
+    glens = [int(x) for x in seq_lens]  # global lengths
+    assert len(glens) == n_seqs
+    if ctx_shard is not None:
+        from .shard import context_shard
+        segs = [context_shard(L, ctx_shard[0], ctx_shard[1], PAGE) for L in glens]
+    else:
+        segs = [(0, L) for L in glens]
+    lens = [b - a for a, b in segs]  # lengths held by this cache
     n_rep = n_q_heads // n_kv_heads
     ch_scale = outlier_channel_scale(n_kv_heads, head_dim, cpu_gen)
     query_all = torch.randn(n_seqs, n_q_heads, head_dim, generator=cpu_gen)
@@ -136,7 +146,7 @@ def build(name: str, *, n_seqs: int, n_q_heads: int, n_kv_heads: int, head_dim: 
     ch_scale_dev = ch_scale[hs].to(device)
 
     blocks_per_seq = [(L + PAGE - 1) // PAGE + extra_blocks_per_seq for L in lens]
-    max_blocks = max(blocks_per_seq)
+    max_blocks = max(1, max(blocks_per_seq))
     total_blocks = sum(blocks_per_seq)
     if shuffle_pages:
         perm = torch.randperm(total_blocks, generator=cpu_gen).to(torch.int32)
@@ -151,15 +161,19 @@ def build(name: str, *, n_seqs: int, n_q_heads: int, n_kv_heads: int, head_dim: 
     bt_dev = bt.to(device)
 
     dgen = torch.Generator(device=device)
-    for s, L in enumerate(lens):
+    for s, L in enumerate(glens):
+        a0, b0 = segs[s]
         for c0 in range(0, L, chunk_tokens):
             n = min(chunk_tokens, L - c0)
+            lo, hi = max(a0, c0), min(b0, c0 + n)
+            if hi <= lo:
+                continue
             dgen.manual_seed((seed * 1000003 + s) * 4099 + c0 // chunk_tokens)
             kv = torch.randn(2, n, n_kv_heads, head_dim, generator=dgen, device=device,
                              dtype=torch.float32)
-            k = (kv[0, :, hs] * ch_scale_dev).to(kv_dtype)
-            v = (kv[1, :, hs] * ch_scale_dev).to(kv_dtype)
-            pos = torch.arange(c0, c0 + n, device=device)
+            k = (kv[0, lo - c0:hi - c0, hs] * ch_scale_dev).to(kv_dtype)
+            v = (kv[1, lo - c0:hi - c0, hs] * ch_scale_dev).to(kv_dtype)
+            pos = torch.arange(lo - a0, hi - a0, device=device)  # positions in this cache
             slots = bt_dev[s, pos // PAGE].to(torch.int64) * PAGE + (pos % PAGE)
             append_tokens(caches, k, v, slots, k_mode, v_mode)
     kc, vc, ks, vs, kz, vz = caches
@@ -171,7 +185,8 @@ def build(name: str, *, n_seqs: int, n_q_heads: int, n_kv_heads: int, head_dim: 
 
 
 def config(name: str, device, *, seed: Optional[int] = None, scale: float = 1.0,
-           head_slice: Optional[slice] = None, extra_blocks_per_seq: int = 0) -> Workload:
+           head_slice: Optional[slice] = None, extra_blocks_per_seq: int = 0,
+           ctx_shard: Optional[tuple] = None) -> Workload:
     """The named benchmark configurations.  ``scale`` < 1 shrinks context lengths
     (and nothing else) for tests; ``extra_blocks_per_seq`` reserves spare pages per
     sequence for tokens appended later.
@@ -189,7 +204,8 @@ def config(name: str, device, *, seed: Optional[int] = None, scale: float = 1.0,
     if name == "gpt2_mha_1k":
         return build(name, n_seqs=1, n_q_heads=12, n_kv_heads=12, head_dim=64, seq_lens=[ctx(1024)],
                      seed=1000 if seed is None else seed, device=device, kv_dtype=torch.float32,
-                     q_dtype=torch.float32, head_slice=head_slice, extra_blocks_per_seq=extra_blocks_per_seq)
+                     q_dtype=torch.float32, head_slice=head_slice, extra_blocks_per_seq=extra_blocks_per_seq,
+                     ctx_shard=ctx_shard)
     import re
     m = re.fullmatch(r"llama8b_b(\d+)_(\d+)k", name)
     if m and name != "llama8b_b1_384k":
@@ -197,22 +213,26 @@ def config(name: str, device, *, seed: Optional[int] = None, scale: float = 1.0,
         B, T = int(m.group(1)), int(m.group(2)) * 1024
         return build(name, n_seqs=B, n_q_heads=32, n_kv_heads=8, head_dim=128,
                      seq_lens=[ctx(T)] * B, seed=2000 if seed is None else seed, device=device,
-                     head_slice=head_slice, extra_blocks_per_seq=extra_blocks_per_seq)
+                     head_slice=head_slice, extra_blocks_per_seq=extra_blocks_per_seq,
+                     ctx_shard=ctx_shard)
     if name == "llama8b_b1_384k":
         return build(name, n_seqs=1, n_q_heads=32, n_kv_heads=8, head_dim=128,
                      seq_lens=[ctx(393216)], seed=3000 if seed is None else seed, device=device,
-                     head_slice=head_slice, extra_blocks_per_seq=extra_blocks_per_seq)
+                     head_slice=head_slice, extra_blocks_per_seq=extra_blocks_per_seq,
+                     ctx_shard=ctx_shard)
     if name == "llama70b_ragged":
         g = torch.Generator().manual_seed(4000 if seed is None else seed)
         lens = torch.randint(1024, 32769, (64,), generator=g).tolist()
         return build(name, n_seqs=64, n_q_heads=64, n_kv_heads=8, head_dim=128,
                      seq_lens=[ctx(L) for L in lens], seed=4000 if seed is None else seed,
-                     device=device, shuffle_pages=True, head_slice=head_slice, extra_blocks_per_seq=extra_blocks_per_seq)
+                     device=device, shuffle_pages=True, head_slice=head_slice, extra_blocks_per_seq=extra_blocks_per_seq,
+                     ctx_shard=ctx_shard)
     if name == "mixed_k8v4":
         g = torch.Generator().manual_seed(5000 if seed is None else seed)
         lens = torch.randint(512, 4097, (128,), generator=g).tolist()
         return build(name, n_seqs=128, n_q_heads=32, n_kv_heads=8, head_dim=128,
                      seq_lens=[ctx(L) for L in lens], seed=5000 if seed is None else seed,
                      device=device, k_mode="int8", v_mode="int4_asym", shuffle_pages=True,
-                     head_slice=head_slice, extra_blocks_per_seq=max(4, extra_blocks_per_seq))
+                     head_slice=head_slice, extra_blocks_per_seq=max(4, extra_blocks_per_seq),
+                     ctx_shard=ctx_shard)
     raise ValueError(f"unknown workload {name}")

@@ -346,6 +346,39 @@ def test_combine_vs_oracle(cuda_device):
     np.testing.assert_allclose(out3.cpu().numpy(), ref, atol=1e-5, rtol=1e-5)
 
 
+@pytest.mark.parametrize("world", [2, 8])
+def test_context_shard_on_one_gpu(world, cuda_device):
+    """The context-shard path with the ranks emulated one after the other on one
+    GPU: every 'rank' decodes its contiguous, page-aligned token segment (its own
+    view of the block table and local lengths), packs ONE partial per (sequence,
+    q head); the stacked partials (what the all-gather would deliver) are merged."""
+    from knlp_b200 import ops, shard, workloads
+    w = workloads.config("llama8b_b1_384k", cuda_device, scale=0.03)  # 11 796 tokens
+    w2 = workloads.build("ragged", n_seqs=3, n_q_heads=32, n_kv_heads=8, head_dim=128,
+                         seq_lens=[5000, 17, 900], seed=9, device=cuda_device, shuffle_pages=True)
+    for wl in (w, w2):
+        ref = _workload_oracle(wl)
+        kp = ops._plane(wl.key_cache, wl.k_scales, wl.k_zeros, ops._lib.KV_INT4_ASYM)
+        vp = ops._plane(wl.value_cache, wl.v_scales, wl.v_zeros, ops._lib.KV_INT4_ASYM)
+        packed = []
+        for r in range(world):
+            segs = [shard.context_shard(L, world, r, 16) for L in wl.seq_lens_host]
+            first_page = [a // 16 for a, _ in segs]
+            max_pages = max((b - a + 15) // 16 for a, b in segs) or 1
+            bt = torch.zeros(wl.n_seqs, max_pages, dtype=torch.int32)
+            full = wl.block_table.cpu()
+            for s, (a, b) in enumerate(segs):
+                n = (b - a + 15) // 16
+                bt[s, :n] = full[s, first_page[s]:first_page[s] + n]
+            lens = torch.tensor([b - a for a, b in segs], dtype=torch.int32, device=cuda_device)
+            pm, pl, po = ops.decode_partials(wl.query, kp, vp, wl.key_cache.shape[0],
+                                             bt.to(cuda_device), lens, wl.n_kv_heads, wl.head_dim, 16,
+                                             max_seq_len=int(max(b - a for a, b in segs)))
+            packed.append(ops.combine_to_packed(pm, pl, po))
+        out = ops.combine_packed(torch.stack(packed))
+        assert_close(out.cpu().numpy(), ref, f"context shard x{world}")
+
+
 def test_zz_device_status_is_clean(cuda_device):
     """No kernel of this session gave up on a barrier wait."""
     from knlp_b200 import ops
