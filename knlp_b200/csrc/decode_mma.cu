@@ -83,6 +83,9 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int sr
                "r"(src_bytes)
                : "memory");
 }
+__device__ __forceinline__ void cp_async16_full(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
+}
 __device__ __forceinline__ void cp_async8(uint32_t dst, const void* src, int src_bytes) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;\n" ::"r"(dst), "l"(src),
                "r"(src_bytes)
@@ -505,7 +508,31 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
       cp_async16(s_dst + stage_off, src, live ? 16 : 0);
     }
   };
+  // Fast path for the common stage: it lies inside one page (TT <= block size) and
+  // entirely before the end of the sequence.  One page lookup, one base address per
+  // array, constant steps between a thread's pieces, no predicates.
+  const bool one_page = TT <= (1 << mp.page_log2);
+  const uint32_t k_step = static_cast<uint32_t>(k_dtt) * kcs1;
+  const uint32_t v_step = static_cast<uint32_t>(v_dtt) * vcs1;
   auto issue_stage = [&](int it) {
+    const int stage_tok0 = start + it * TT;
+    if (one_page && stage_tok0 + TT <= end) {
+      const int raw = pg_tab[it % (kStages + 1)][0];
+      const uint32_t blk = static_cast<uint32_t>(raw < 0 ? 0 : (raw > max_blk ? max_blk : raw));
+      const uint32_t off_s = static_cast<uint32_t>(stage_tok0 & page_mask);
+      const uint32_t stage_off = static_cast<uint32_t>(it % kStages) * G::kStageBytes;
+      const uint8_t* kb = k_src0 + (static_cast<uint64_t>(blk) * kcs0 + (off_s + k_tt0) * kcs1);
+#pragma unroll
+      for (int n = 0; n < kKPer; ++n) cp_async16_full(k_dst[n] + stage_off, kb + n * k_step);
+      const uint8_t* vb = v_src0 + (static_cast<uint64_t>(blk) * vcs0 + (off_s + v_tt0) * vcs1);
+#pragma unroll
+      for (int n = 0; n < kVPer; ++n) cp_async16_full(v_dst[n] + stage_off, vb + n * v_step);
+      if (s_on) {
+        const uint8_t* sb = s_src0 + (static_cast<uint64_t>(blk) * s_st0 + (off_s + s_tt) * s_st1);
+        cp_async16_full(s_dst + stage_off, sb);
+      }
+      return;
+    }
     issue_part(it, 0);
     issue_part(it, 1);
     issue_part(it, 2);
