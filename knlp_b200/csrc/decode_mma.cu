@@ -290,7 +290,8 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
   // swizzled TMA tiles need their natural alignment: round the base up to 1 KB
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   __shared__ __align__(8) uint64_t bars[2 * kStages];  // full[0..kStages), empty[...]
-  __shared__ int pg_tab[kStages + 1][16];              // page ids of the stages in flight
+  static_assert(kStages < 8, "the page table ring has 8 slots");
+  __shared__ int pg_tab[8][16];  // page ids of the stages in flight (ring, slot = stage & 7)
 
   const int tid = threadIdx.x;
   const int lane = tid & 31;
@@ -477,7 +478,7 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
   auto issue_part = [&](int it, int part) {
     const int stage_tok0 = start + it * TT;
     const int page0 = stage_tok0 >> mp.page_log2;
-    const int slot = it % (kStages + 1);
+    const int slot = it & 7;
     const uint32_t stage_off = static_cast<uint32_t>(it % kStages) * G::kStageBytes;
     if (part == 0) {
 #pragma unroll
@@ -517,7 +518,7 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
   auto issue_stage = [&](int it) {
     const int stage_tok0 = start + it * TT;
     if (one_page && stage_tok0 + TT <= end) {
-      const int raw = pg_tab[it % (kStages + 1)][0];
+      const int raw = pg_tab[it & 7][0];
       const uint32_t blk = static_cast<uint32_t>(raw < 0 ? 0 : (raw > max_blk ? max_blk : raw));
       const uint32_t off_s = static_cast<uint32_t>(stage_tok0 & page_mask);
       const uint32_t stage_off = static_cast<uint32_t>(it % kStages) * G::kStageBytes;
@@ -743,7 +744,7 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
       cp_async_wait<kStages - 2>();
       __syncthreads();
       if (tid < 16) {
-        pg_tab[(it + kStages) % (kStages + 1)][tid] = pg_reg;  // loaded one iteration ago
+        pg_tab[(it + kStages) & 7][tid] = pg_reg;  // loaded one iteration ago
         pg_reg = load_pages(it + kStages + 1);
       }
     }
@@ -838,7 +839,6 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
           for (int g = 0; g < NG; ++g) kz[g] = (kInt8K ? -128.0f : -8.0f) * ks[g];
         }
         float c0 = 0.0f, c1 = 0.0f;  // columns 2ft, 2ft+1 (still scaled by 2^-24)
-        const bool valid = (tok0 + fr + rh * 8) < end;
         if constexpr (SPLIT) {
           // hi and lo columns of one head share scale and zero: add them first
 #pragma unroll
@@ -846,7 +846,7 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
             c0 = fmaf(ks[g], sacc[g][2 * rh] + sacc[g][2 * rh + 1], c0);
             c1 = fmaf(kz[g], qsum[g][0], c1);
           }
-          sc[rh][0] = valid ? (c0 + c1) * score_mul : -INFINITY;
+          sc[rh][0] = (c0 + c1) * score_mul;
         } else {
 #pragma unroll
           for (int g = 0; g < NG; ++g) {
@@ -855,8 +855,17 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
             c0 = fmaf(kz[g], qsum[g][0], c0);
             c1 = fmaf(kz[g], qsum[g][1], c1);
           }
-          sc[rh][0] = valid ? c0 * score_mul : -INFINITY;
-          sc[rh][1] = valid ? c1 * score_mul : -INFINITY;
+          sc[rh][0] = c0 * score_mul;
+          sc[rh][1] = c1 * score_mul;
+        }
+      }
+      if (partial) {  // warp-uniform: only the last tile of a split masks rows
+#pragma unroll
+        for (int rh = 0; rh < 2; ++rh) {
+          if (tok0 + fr + rh * 8 >= end) {
+#pragma unroll
+            for (int h = 0; h < NH; ++h) sc[rh][h] = -INFINITY;
+          }
         }
       }
     }
