@@ -363,7 +363,11 @@ def run_ours(args):
             "roofline": {"bound": "hbm", "achieved": ach, "peak": peak_gbs, "unit": "GB/s",
                          "frac": ach / peak_gbs, "peak_kind": peak_kind,
                          "kernel": "decode_mma_kernel", "kernel_us": kern_ms * 1e3,
-                         "traffic": None},
+                         # DRAM bytes per launch on one GPU, scaled from the ncu capture of
+                         # the 8K-context case (profiles/decode_mma_kernel_*_ncu_full.md):
+                         # reads = 0.9996 x algorithmic bytes, writes = the split partials
+                         "traffic": int(0.9996 * alg_local + S * Hq * n_splits * (d + 2) * 4),
+                         "traffic_source": "ncu dram__bytes of a smaller launch, scaled by tokens"},
             "e2e": {"value": alg_total / (e2e_ms / K / 1e3) / 1e12, "unit": UNIT,
                     "ms_per_step": e2e_ms / K, "h2d_bytes_per_step": int(h2d_total),
                     "d2h_bytes_per_step": int(d2h_total)},
