@@ -10,7 +10,8 @@
  * Every entry point is plain C: raw device pointers, sizes, strides and a
  * cudaStream_t passed as void*.  Nothing here allocates or synchronises except
  * where a comment says so; all launches go to the given stream, so the calls are
- * stream-ordered and capturable.  Return value: 0 on success, a negative
+ * stream-ordered and (knlp_b200_decode_noalloc aside, which carries its own notes)
+ * capturable.  Return value: 0 on success, a negative
  * knlp_status on an argument error detected on the host before any launch.
  *
  * Reference interfaces replaced (mcgrof/knlp, fused-quant/fused_int4.v0.1.0.py):
@@ -169,6 +170,38 @@ int knlp_b200_combine(const float* part_m, const float* part_l, const float* par
                       void* out, int out_dtype, int64_t out_row_stride,
                       float* out_m, float* out_l, int64_t out_ml_stride,
                       int n_rows, int head_dim, void* stream);
+
+/*
+ * Decode attention straight to the output, with NO device allocation by anyone.
+ * It has no counterpart in the reference.  It exists for hosts that cannot hand
+ * knlp_b200_decode_splitk a workspace: an engine that gave all device memory to its
+ * own pool at start-up and may not call cudaMalloc any more, or a C / Go / Java
+ * host without a device allocator.  The split partials live in a fixed array of
+ * KNLP_NOALLOC_MAX_FLOATS floats (32 MiB) inside the library, present on every GPU
+ * that loads it until the process exits.
+ *   arguments   as knlp_b200_decode_splitk, plus the output of knlp_b200_combine:
+ *               out [n_seqs * n_q_heads, head_dim] of out_dtype, row stride
+ *               out_row_stride elements
+ *   n_splits    > 0: used as given; <= 0: chosen by the library and reduced to what
+ *               the fixed array holds
+ *   limit       n_seqs * n_q_heads * n_splits * (head_dim + 2) must not exceed
+ *               KNLP_NOALLOC_MAX_FLOATS, else KNLP_ERR_TOO_LARGE is returned and
+ *               nothing is launched
+ * The first call on a device looks up the array's device address (no allocation);
+ * make that first call outside any stream capture.  All calls on a device share the
+ * array: two calls whose kernels may overlap on the GPU (different streams) race on
+ * it, so keep them on one stream or order them with events.  The array keeps the
+ * last call's partials; every value a call reads it has written itself, so nothing
+ * needs clearing in between.
+ */
+#define KNLP_NOALLOC_MAX_FLOATS (8ll << 20)
+int knlp_b200_decode_noalloc(const void* query, int q_dtype, const int64_t q_stride[2],
+                             const knlp_kv_plane* k_plane, const knlp_kv_plane* v_plane,
+                             const int32_t* block_table, int64_t bt_stride,
+                             const int32_t* seq_lens, int64_t num_blocks,
+                             int n_seqs, int n_q_heads, int n_kv_heads, int head_dim,
+                             int block_size, int n_splits, int max_seq_len,
+                             void* out, int out_dtype, int64_t out_row_stride, void* stream);
 
 #ifdef __cplusplus
 }
