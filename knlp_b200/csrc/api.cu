@@ -109,19 +109,20 @@ int knlp_b200_decode_plan(int n_seqs, int n_q_heads, int n_kv_heads, int head_di
   if (n_seqs <= 0 || n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads)
     return KNLP_ERR_SHAPE;
   if (!head_dim_ok(head_dim) || max_seq_len < 0) return KNLP_ERR_SHAPE;
-  // CTAs per split: one per (sequence, block of up to 8 kv heads).  Two CTAs fit on
-  // an SM.  Pick the split count that fills whole waves best; prefer at least two
-  // waves so the tail is amortised, and never go below 256 tokens per split.
-  int hpb = 8;
+  // CTAs per split: one per (sequence, block of up to kDecodeWarps kv heads);
+  // kDecodeCtasPerSm of them fit on an SM.  Pick the split count that fills whole waves
+  // best; prefer at least two waves so the tail is amortised, and never go below 256
+  // tokens per split.
+  int hpb = kDecodeWarps;
   while (hpb > 1 && n_kv_heads % hpb) hpb >>= 1;
   const int64_t base = static_cast<int64_t>(n_seqs) * (n_kv_heads / hpb);
-  const int64_t slots = 2LL * sm_count();
+  const int64_t slots = static_cast<int64_t>(kDecodeCtasPerSm) * sm_count();
   const int max_splits = max_seq_len >= 512 ? (max_seq_len / 256 > 1024 ? 1024 : max_seq_len / 256) : 1;
   // Cost model (microseconds, coarse, measured on B200): a wave of CTAs costs a fixed
-  // set-up plus 1.4 us per 16-token x 8-head stage of its split; merging costs a
+  // set-up plus 1.2 us per stage (16 tokens x the CTA's heads) of its split; merging costs a
   // little per split.  Fewer, longer splits amortise the set-up; more splits fill the
   // machine and even out ragged batches.
-  const int tokens_per_stage = 16 * (8 / hpb);
+  const int tokens_per_stage = 16 * (kDecodeWarps / hpb);
   int best = 1;
   double best_cost = 1e30;
   for (int n = 1; n <= max_splits; ++n) {
@@ -130,7 +131,7 @@ int knlp_b200_decode_plan(int n_seqs, int n_q_heads, int n_kv_heads, int head_di
     if (waves > 8 && n > 1) break;
     const int chunk = split_chunk(max_seq_len, n);
     const double stages = static_cast<double>((chunk + tokens_per_stage - 1) / tokens_per_stage);
-    const double cost = static_cast<double>(waves) * (6.0 + 1.4 * stages) + 0.03 * n + 3.0;
+    const double cost = static_cast<double>(waves) * (6.0 + 1.2 * stages) + 0.03 * n + 3.0;
     if (cost < best_cost - 1e-9) {
       best_cost = cost;
       best = n;

@@ -103,6 +103,16 @@ int launch_decode_generic(const DecodeArgs& a, cudaStream_t st);
 // tensor-core kernel (caller falls back to the generic one), <0 on error.
 // allow_tma = false keeps the tensor-core kernel on its cp.async loader.
 int launch_decode_mma(const DecodeArgs& a, bool allow_tma, cudaStream_t st);
+
+// CTA shape of the tensor-core decode kernel, shared with the split planner: one warp
+// per (kv head, 16-token tile), so a CTA covers at most kDecodeWarps kv heads; sixteen
+// warps of ~128 registers fit on an SM.  Four CTAs of four warps measured faster than
+// two of eight (the CTAs of an SM wait at their stage barriers independently).
+#ifndef KNLP_WARPS
+#define KNLP_WARPS 4
+#endif
+constexpr int kDecodeWarps = KNLP_WARPS;  // 8, 4 or 2
+constexpr int kDecodeCtasPerSm = 16 / kDecodeWarps;
 // Device-side status word of the decode kernels (0 = clean); synchronises.
 int read_and_clear_decode_status();
 

@@ -47,6 +47,7 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <type_traits>
 #include <vector>
 
 #include "common.cuh"
@@ -66,7 +67,9 @@ int read_and_clear_decode_status() {
 
 namespace {
 
-constexpr int kWarpsCta = 8;
+constexpr int kWarpsCta = kDecodeWarps;
+constexpr int kWarpsLog = kWarpsCta == 8 ? 3 : kWarpsCta == 4 ? 2 : 1;
+constexpr int kCtasPerSm = kDecodeCtasPerSm;
 constexpr int kThreads = kWarpsCta * 32;
 #ifndef KNLP_STAGES
 #define KNLP_STAGES 4
@@ -78,13 +81,26 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// .ca (allocate in L1) rather than .cg: measured 5 % faster here, the fills reach
+// shared memory in fewer, wider writes.  The data is streamed once either way.
+#ifdef KNLP_CP_CG
+#define KNLP_CP_MODE "cg"
+#else
+#define KNLP_CP_MODE "ca"
+#endif
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src),
+  asm volatile("cp.async." KNLP_CP_MODE ".shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src),
                "r"(src_bytes)
                : "memory");
 }
 __device__ __forceinline__ void cp_async16_full(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
+  asm volatile("cp.async." KNLP_CP_MODE ".shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
+}
+template <int OFF>  // destination = dst + OFF, the offset folded into the address operand
+__device__ __forceinline__ void cp_async16_full_at(uint32_t dst, const void* src) {
+  asm volatile("cp.async." KNLP_CP_MODE ".shared.global [%0+%2], [%1], 16;\n" ::"r"(dst), "l"(src),
+               "n"(OFF)
+               : "memory");
 }
 __device__ __forceinline__ void cp_async8(uint32_t dst, const void* src, int src_bytes) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;\n" ::"r"(dst), "l"(src),
@@ -113,6 +129,19 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t r[4]) 
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                : "r"(addr));
+}
+// the same with a compile-time byte offset folded into the address operand
+template <int OFF>
+__device__ __forceinline__ void ldmatrix_x4_at(uint32_t addr, uint32_t r[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4+%5];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr), "n"(OFF));
+}
+template <int OFF>
+__device__ __forceinline__ void ldmatrix_x4_trans_at(uint32_t addr, uint32_t r[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4+%5];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr), "n"(OFF));
 }
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
   uint32_t d;
@@ -272,13 +301,26 @@ struct MmaParams {
   int page_log2;  // block_size = 1 << page_log2
 };
 
+// Calls f(it0 + S, integral_constant<S>) for S = FIRST .. N-1 while it0 + S < n; stops
+// and returns false as soon as a call does.
+template <int S, int N, class F>
+__device__ __forceinline__ bool run_stages(F& f, int it0, int n) {
+  if constexpr (S < N) {
+    if (it0 + S >= n) return true;
+    if (!f(it0 + S, std::integral_constant<int, S>{})) return false;
+    return run_stages<S + 1, N>(f, it0, n);
+  } else {
+    return true;
+  }
+}
+
 // TMA = true: stages are filled by cp.async.bulk.tensor copies issued by one warp
 // per iteration (the warps take turns) and handed over through full/empty
 // mbarriers; the warps never meet at a CTA barrier inside the main loop.
 // TMA = false: stages are filled by cp.async from all threads (any 16-byte
 // aligned strides), one __syncthreads per stage.
-template <int HD, int KMODE, int VMODE, bool SPLIT, bool TMA>
-__global__ void __launch_bounds__(kThreads, 2)
+template <int HD, int KMODE, int VMODE, bool SPLIT, bool TMA, int HPBL>
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
 decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant__ TmaMaps tm) {
   using G = Geo<HD, KMODE, TMA ? 0 : 16>;
   constexpr int NG = G::NG;
@@ -289,7 +331,8 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
   extern __shared__ uint8_t smem_raw[];
   // swizzled TMA tiles need their natural alignment: round the base up to 1 KB
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  __shared__ __align__(8) uint64_t bars[2 * kStages];  // full[0..kStages), empty[...]
+  __shared__ __align__(8) uint64_t bars[kStages];  // TMA path: "stage has landed" barriers
+  __shared__ unsigned slot_done[kStages];          // TMA path: warps finished with the slot
   static_assert(kStages < 8, "the page table ring has 8 slots");
   __shared__ int pg_tab[8][16];  // page ids of the stages in flight (ring, slot = stage & 7)
 
@@ -299,9 +342,9 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
   const int fr = lane >> 2;  // fragment row / column-of-B index
   const int ft = lane & 3;   // fragment quad index
 
-  const int hpb_log2 = mp.hpb_log2;
-  const int HPB = 1 << hpb_log2;
-  const int TT = (kWarpsCta >> hpb_log2) * 16;  // tokens per stage
+  constexpr int hpb_log2 = HPBL;  // kv heads per CTA = 1 << HPBL, a compile-time constant
+  constexpr int HPB = 1 << hpb_log2;
+  constexpr int TT = (kWarpsCta >> hpb_log2) * 16;  // tokens per stage
   const int split = blockIdx.x;
   const int hb = blockIdx.y;
   const int seq = blockIdx.z;
@@ -439,7 +482,7 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
   // Scales and zeros: each array of a stage is 128 rows of SB bytes laid out
   // [token][head], also copied in 16-byte pieces in memory order; thread tid serves
   // array tid / (8 * SB) (ks, kz, vs, vz), piece tid % (8 * SB).
-  constexpr int kSPieces = 8 * G::SB;  // per array and stage
+  constexpr int kSPieces = kRows * G::SB / 16;  // per array and stage
   const int s_arr = tid / kSPieces;
   const int s_byte = (tid % kSPieces) * 16;        // byte offset inside the stage's array
   const int s_tb = G::SB << hpb_log2;              // bytes of one token's row (CTA's heads)
@@ -453,10 +496,21 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
                           (hb * s_tb + (s_tb >= 16 ? s_byte % s_tb : 0));
   const uint32_t s_st0 = s_on ? static_cast<uint32_t>(s_st[0]) * 2 : 0;  // bytes
   const uint32_t s_st1 = s_on ? static_cast<uint32_t>(s_st[1]) * 2 : 0;
+  // A warp later reads the 8 rows fr = 0..7 of ONE head in a single instruction; with
+  // token rows of 32 or 64 bytes these would fall on the same banks (2- or 4-way
+  // conflict).  So the 16-byte pieces of token row t are stored xor-permuted by the
+  // row's index within the 128-byte bank period (see sc_swz below).
+  constexpr int s_tb_log = hpb_log2 + (G::SB == 8 ? 3 : 2);
+  auto sc_swz = [&](int t, int byte_in_row) -> int {
+    if (TMA || s_tb_log < 5) return byte_in_row;  // TMA boxes land unpermuted
+    constexpr int kPieceLog = s_tb_log >= 5 ? s_tb_log - 4 : 0;  // 16-byte pieces per row
+    constexpr int kPeriodLog = s_tb_log >= 5 ? 7 - s_tb_log : 0;  // rows per 128 bytes
+    return byte_in_row ^ (((t >> kPeriodLog) & ((1 << kPieceLog) - 1)) << 4);
+  };
   const uint32_t s_dst =
       smem_base + (s_arr == 0 ? G::kOffKs : s_arr == 1 ? G::kOffKz : s_arr == 2 ? G::kOffVs
                                                                                : G::kOffVz) +
-      s_byte;
+      (s_tb_log >= 5 ? s_tt * s_tb + sc_swz(s_tt, s_byte % s_tb) : s_byte);
 
   // Page ids reach the copiers through a small table in shared memory: 16 threads
   // load the ids of a stage two iterations before it is issued and park them in a
@@ -475,11 +529,10 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
   // The copies of a stage: part 0 = K codes, 1 = V codes, 2 = scales and zeros.  They
   // are all issued at the top of an iteration (spreading them over the iteration
   // measured slower).
-  auto issue_part = [&](int it, int part) {
+  auto issue_part = [&](int it, int part, uint32_t stage_off) {
     const int stage_tok0 = start + it * TT;
     const int page0 = stage_tok0 >> mp.page_log2;
     const int slot = it & 7;
-    const uint32_t stage_off = static_cast<uint32_t>(it % kStages) * G::kStageBytes;
     if (part == 0) {
 #pragma unroll
       for (int n = 0; n < kKPer; ++n) {
@@ -515,35 +568,35 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
   const bool one_page = TT <= (1 << mp.page_log2);
   const uint32_t k_step = static_cast<uint32_t>(k_dtt) * kcs1;
   const uint32_t v_step = static_cast<uint32_t>(v_dtt) * vcs1;
-  auto issue_stage = [&](int it) {
+  auto issue_stage = [&](int it, auto stage_tag) {  // stage_tag: it % kStages as a constant
+    constexpr int stage_off = decltype(stage_tag)::value * G::kStageBytes;
     const int stage_tok0 = start + it * TT;
     if (one_page && stage_tok0 + TT <= end) {
       const int raw = pg_tab[it & 7][0];
       const uint32_t blk = static_cast<uint32_t>(raw < 0 ? 0 : (raw > max_blk ? max_blk : raw));
       const uint32_t off_s = static_cast<uint32_t>(stage_tok0 & page_mask);
-      const uint32_t stage_off = static_cast<uint32_t>(it % kStages) * G::kStageBytes;
       const uint8_t* kb = k_src0 + (static_cast<uint64_t>(blk) * kcs0 + (off_s + k_tt0) * kcs1);
 #pragma unroll
-      for (int n = 0; n < kKPer; ++n) cp_async16_full(k_dst[n] + stage_off, kb + n * k_step);
+      for (int n = 0; n < kKPer; ++n) cp_async16_full_at<stage_off>(k_dst[n], kb + n * k_step);
       const uint8_t* vb = v_src0 + (static_cast<uint64_t>(blk) * vcs0 + (off_s + v_tt0) * vcs1);
 #pragma unroll
-      for (int n = 0; n < kVPer; ++n) cp_async16_full(v_dst[n] + stage_off, vb + n * v_step);
+      for (int n = 0; n < kVPer; ++n) cp_async16_full_at<stage_off>(v_dst[n], vb + n * v_step);
       if (s_on) {
         const uint8_t* sb = s_src0 + (static_cast<uint64_t>(blk) * s_st0 + (off_s + s_tt) * s_st1);
-        cp_async16_full(s_dst + stage_off, sb);
+        cp_async16_full_at<stage_off>(s_dst, sb);
       }
       return;
     }
-    issue_part(it, 0);
-    issue_part(it, 1);
-    issue_part(it, 2);
+    issue_part(it, 0, stage_off);
+    issue_part(it, 1, stage_off);
+    issue_part(it, 2, stage_off);
   };
 
   const int n_iters = (end - start + TT - 1) / TT;
 
   // ---------------- TMA path: one warp fills a whole stage ----------------
   const uint32_t bar0 = smem_u32(bars);
-  const int tiles = kWarpsCta >> hpb_log2;  // 16-token tiles per stage
+  constexpr int tiles = kWarpsCta >> hpb_log2;  // 16-token tiles per stage
   constexpr int kScaleArrays = 2 + (kAsymK ? 1 : 0) + (kAsymV ? 1 : 0);
   // bytes one live tile (16 tokens x HPB heads) brings into a stage
   const uint32_t tile_bytes =
@@ -566,56 +619,58 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
     return tl * 16 * seg + rho * 128 + ((((off >> 4) & 7) ^ (rho & 7)) << 4);
   };
 
-  // Page ids for the stage this warp fills NEXT (8 iterations from now) are loaded at
-  // the end of the current fill, so that a fill never waits on the page table.
-  int pg_pref[2] = {0, 0};
-  int pg_pref_it = -1;
-  const int nk = tiles * k_box, nv = tiles * v_box;  // K and V boxes per stage
-  const int n_copies = nk + nv + 4 * tiles;
-  auto tile_of_copy = [&](int c) -> int {
-    if (c < nk) return c / k_box;
-    if (c < nk + nv) return (c - nk) / v_box;
-    return (c - nk - nv) & (tiles - 1);
+  // A stage is K, V, ks, kz, vs, vz boxes for each of its 16-token tiles; lane c of the
+  // issuing warp owns copies c and c + 32.  Every warp keeps, for its own copies, the
+  // page ids of the stage that will next land in the slot it is working on (loaded at
+  // the top of the iteration, used at its end), so a refill never waits on the table.
+  constexpr int n_copies = 6 * tiles;
+  constexpr int kCopySlots = (n_copies + 31) / 32;
+  int pg_next[kCopySlots];
+  auto copy_tok = [&](int it, int c) -> int { return start + it * TT + (c & (tiles - 1)) * 16; };
+  auto prefetch_pages = [&](int it) {
+#pragma unroll
+    for (int j = 0; j < kCopySlots; ++j) {
+      // The address is clamped, not the result: nothing may depend on the loaded value
+      // here, or the warp (which issues in order) would sit out the load's latency.
+      const int tok = min(copy_tok(it, lane + 32 * j), end - 1);
+      pg_next[j] = __ldg(bt_row + (tok >> mp.page_log2));
+    }
   };
-  auto issue_tma = [&](int it) {
-    const int sn = it % kStages;
+  auto issue_tma = [&](int it, auto stage_tag, bool prefetched) {
+    constexpr int sn = decltype(stage_tag)::value;  // == it % kStages
     const int stage_tok0 = start + it * TT;
     const int live_tiles = min(tiles, (end - stage_tok0 + 15) >> 4);
     const uint32_t full = bar0 + sn * 8;
     if (lane == 0) mbar_arrive_expect_tx(full, static_cast<uint32_t>(live_tiles) * tile_bytes);
     __syncwarp();
     const uint32_t stage_base = smem_base + static_cast<uint32_t>(sn) * G::kStageBytes;
-    // a lane owns copies lane and lane + 32 of the stage's boxes
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
+    for (int j = 0; j < kCopySlots; ++j) {
       const int c = lane + 32 * j;
       if (c >= n_copies) continue;
-      const int tl = tile_of_copy(c);
+      const int tl = c & (tiles - 1);
       if (tl >= live_tiles) continue;
       const int tok = stage_tok0 + tl * 16;
-      int blk = (pg_pref_it == it) ? pg_pref[j] : __ldg(bt_row + (tok >> mp.page_log2));
+      int blk = prefetched ? pg_next[j] : __ldg(bt_row + (tok >> mp.page_log2));
       blk = blk < 0 ? 0 : (blk > max_blk ? max_blk : blk);
       const int off = tok & page_mask;
-      if (c < nk + nv) {
-        const bool is_v = c >= nk;
-        const int cc = is_v ? c - nk : c;
+      const int arr = c / tiles;  // 0 K codes, 1 V codes, 2 ks, 3 kz, 4 vs, 5 vz
+      if (arr < 2) {
+        const bool is_v = arr == 1;
         const int nbox = is_v ? v_box : k_box;
         const int seg = is_v ? v_seg : k_seg;
-        const int col = cc % nbox;
         const void* map = is_v ? static_cast<const void*>(&tm.v) : static_cast<const void*>(&tm.k);
         const uint32_t region = stage_base + (is_v ? G::kOffV : G::kOffK);
         if (seg >= 128) {
-          tma_load_4d(region + ((tl * nbox + col) << 11), map, full, 0,
-                      ((hb * seg) >> 7) + col, off, blk);
+          tma_load_4d(region + ((tl * nbox) << 11), map, full, 0, off, (hb * seg) >> 7, blk);
         } else {
           tma_load_3d(region + tl * 16 * seg, map, full, 0, (off * seg) >> 7, blk);
         }
       } else {
-        const int arr = (c - nk - nv) / tiles;  // 0 ks, 1 kz, 2 vs, 3 vz
-        if ((arr == 1 && !kAsymK) || (arr == 3 && !kAsymV)) continue;
-        const void* map = arr == 0 ? &tm.ks : arr == 1 ? &tm.kz : arr == 2 ? &tm.vs : &tm.vz;
+        if ((arr == 3 && !kAsymK) || (arr == 5 && !kAsymV)) continue;
+        const void* map = arr == 2 ? &tm.ks : arr == 3 ? &tm.kz : arr == 4 ? &tm.vs : &tm.vz;
         const int aoff =
-            arr == 0 ? G::kOffKs : arr == 1 ? G::kOffKz : arr == 2 ? G::kOffVs : G::kOffVz;
+            arr == 2 ? G::kOffKs : arr == 3 ? G::kOffKz : arr == 4 ? G::kOffVs : G::kOffVz;
         const uint32_t dst = stage_base + aoff + ((tl * 16 * G::SB) << hpb_log2);
         if (tm.scale_merged) {
           tma_load_3d(dst, map, full, ((off * G::SB) << hpb_log2) >> 2, 0, blk);
@@ -624,18 +679,25 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
         }
       }
     }
-    // prefetch the page ids of this warp's next fill
-    const int nit = it + kWarpsCta;
-    pg_pref_it = nit;
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const int c = lane + 32 * j;
-      pg_pref[j] = 0;
-      if (c < n_copies) {
-        const int tok = start + nit * TT + tile_of_copy(c) * 16;
-        if (tok < end) pg_pref[j] = __ldg(bt_row + (tok >> mp.page_log2));
-      }
+  };
+  // A warp that has finished reading a slot counts itself off; the LAST one to do so
+  // refills the slot at once with the stage kStages ahead.  The acq_rel counter orders
+  // every warp's reads of the slot before the refill that overwrites it.
+  auto release_slot = [&](int it, auto stage_tag) {
+    constexpr int sn = decltype(stage_tag)::value;
+    __syncwarp();
+    int last = 0;
+    if (lane == 0) {
+      unsigned old;
+      asm volatile("atom.acq_rel.cta.shared.add.u32 %0, [%1], 1;\n"
+                   : "=r"(old)
+                   : "r"(smem_u32(&slot_done[sn]))
+                   : "memory");
+      last = (old == kWarpsCta - 1) ? 1 : 0;
+      if (last) *reinterpret_cast<volatile unsigned*>(&slot_done[sn]) = 0;
     }
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (last && it + kStages < n_iters) issue_tma(it + kStages, stage_tag, true);
   };
 
   // ---------------- accumulators ----------------
@@ -668,14 +730,18 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
     if (tid == 0) {
 #pragma unroll
       for (int s = 0; s < kStages; ++s) {
-        mbar_init(bar0 + s * 8, 1);                        // full: the issuing lane + tx bytes
-        mbar_init(bar0 + (kStages + s) * 8, kWarpsCta);    // empty: one arrival per warp
+        mbar_init(bar0 + s * 8, 1);  // the issuing lane's arrival + the bytes of the stage
+        slot_done[s] = 0;
       }
       asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     __syncthreads();
     if (warp == 0) {
-      for (int s = 0; s < kStages - 1 && s < n_iters; ++s) issue_tma(s);
+      auto first_fill = [&](int it, auto stage_tag) -> bool {
+        issue_tma(it, stage_tag, false);
+        return true;
+      };
+      run_stages<0, kStages>(first_fill, 0, n_iters);
     }
   } else {
     if (tid < 16) {
@@ -684,11 +750,13 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
       pg_reg = load_pages(kStages);
     }
     __syncthreads();
-#pragma unroll
-    for (int s = 0; s < kStages - 1; ++s) {
-      if (s < n_iters) issue_stage(s);
+    auto first_fill = [&](int it, auto stage_tag) -> bool {
+      issue_stage(it, stage_tag);
       cp_async_commit();
-    }
+      return true;
+    };
+    run_stages<0, kStages - 1>(first_fill, 0, n_iters);
+    for (int s = n_iters; s < kStages - 1; ++s) cp_async_commit();  // keep the group count
   }
 
   // ldmatrix source row of this lane: row (lane & 7) + 8 * ((lane >> 3) & 1), piece + (lane >> 4)
@@ -720,25 +788,25 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
   }
   // scale / zero rows of this thread's two accumulator rows (fr and fr + 8)
   // scale / zero arrays of a stage are [token][head of the CTA] rows of SB bytes
-  const int sc_row0 = ((((w_tile << 4) + fr) << hpb_log2) + w_head) * G::SB;
+  // (the piece permutation of row t depends on t only through bits that rows t and
+  // t + 8 share, so one offset serves both)
+  const int sc_row0 =
+      (((w_tile << 4) + fr) << s_tb_log) + sc_swz((w_tile << 4) + fr, w_head * G::SB);
   const int sc_row8 = (8 * G::SB) << hpb_log2;
 
-  for (int it = 0; it < n_iters; ++it) {
+  // One iteration consumes one stage.  The stage index kS (== it % kStages) is a
+  // compile-time constant, so every shared-memory offset of the body is an immediate;
+  // the driver loop below steps through the stages kStages at a time.  Returns false
+  // if a bounded barrier wait ran out.
+  auto iteration = [&](const int it, auto stage_tag) -> bool {
+    constexpr int kS = decltype(stage_tag)::value;
+    constexpr int kNextS = (kS + kStages - 1) % kStages;  // slot of stage it + kStages - 1
     if constexpr (TMA) {
-      // the warps take turns refilling the slot that iteration it-1 released
-      const int nx = it + kStages - 1;
-      if (warp == (it & (kWarpsCta - 1)) && nx < n_iters) {
-        if (nx >= kStages) {
-          const uint32_t par = static_cast<uint32_t>((nx / kStages) - 1) & 1u;
-          if (!mbar_wait(bar0 + (kStages + nx % kStages) * 8, par)) lost = true;
-        }
-        if (!lost) issue_tma(nx);
-      }
-      if (!mbar_wait(bar0 + (it % kStages) * 8, static_cast<uint32_t>(it / kStages) & 1u))
-        lost = true;
+      prefetch_pages(it + kStages);  // for the refill this warp may issue at the end
+      if (!mbar_wait(bar0 + kS * 8, static_cast<uint32_t>(it / kStages) & 1u)) lost = true;
       if (__any_sync(0xffffffffu, lost)) {
         if (lane == 0) atomicExch(&g_decode_status, 1);
-        break;
+        return false;
       }
     } else {
       cp_async_wait<kStages - 2>();
@@ -750,19 +818,16 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
     }
     if constexpr (!TMA) {
       const int nx = it + kStages - 1;
-      if (nx < n_iters) issue_stage(nx);
+      if (nx < n_iters) issue_stage(nx, std::integral_constant<int, kNextS>{});
       cp_async_commit();
     }
 
-    const uint32_t stage_off = static_cast<uint32_t>(it % kStages) * G::kStageBytes;
+    constexpr int stage_off = kS * G::kStageBytes;
     const uint8_t* st = smem + stage_off;
     const int tok0 = start + it * TT + w_tile * 16;  // first token of this warp's tile
-    const uint32_t empty_bar = bar0 + (kStages + it % kStages) * 8;
     if (tok0 >= end) {  // whole tile past the end (warp-uniform): nothing was loaded for it
-      if constexpr (TMA) {
-        if (lane == 0) mbar_arrive(empty_bar);
-      }
-      continue;
+      if constexpr (TMA) release_slot(it, stage_tag);
+      return true;
     }
     // Rows past the end of a partial tile may hold whatever the page holds there (a TMA
     // box is always whole; a 16-byte scale piece can span two tokens), so their scales
@@ -780,7 +845,7 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
 #pragma unroll
         for (int g = 0; g < NG; ++g) {
           uint32_t w[4];
-          ldmatrix_x4(k_lm[g] + stage_off, w);
+          ldmatrix_x4_at<stage_off>(k_lm[g], w);
           // w0: rows 0-7 piece 2g; w1: rows 8-15 piece 2g; w2/w3: piece 2g+1
           uint32_t lo0[2], hi0[2], lo1[2], hi1[2];
           unpack_int8x4(w[0], lo0);
@@ -794,7 +859,7 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
 #pragma unroll
         for (int gp = 0; gp < NG / 2; ++gp) {
           uint32_t w[4];
-          ldmatrix_x4(k_lm[gp] + stage_off, w);
+          ldmatrix_x4_at<stage_off>(k_lm[gp], w);
           // w0: rows 0-7 group 2gp; w1: rows 8-15 group 2gp; w2/w3: group 2gp+1
 #pragma unroll
           for (int s = 0; s < 2; ++s) {
@@ -944,7 +1009,7 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
 #pragma unroll
     for (int gp = 0; gp < NG / 2; ++gp) {
       uint32_t w[4];
-      ldmatrix_x4_trans(v_lm[gp] + stage_off, w);
+      ldmatrix_x4_trans_at<stage_off>(v_lm[gp], w);
       // w0: tokens 0-7 group 2gp; w1: tokens 8-15 group 2gp; w2/w3: group 2gp+1
 #pragma unroll
       for (int s = 0; s < 2; ++s) {
@@ -972,11 +1037,11 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
         mma16816(oacc[g][1], e0[2], e0[3], e1[2], e1[3], pb[0], pb[1]);
       }
     }
-    if constexpr (TMA) {
-      // this warp is done reading the stage: release its slot to the refilling warp
-      __syncwarp();
-      if (lane == 0) mbar_arrive(empty_bar);
-    }
+    if constexpr (TMA) release_slot(it, stage_tag);  // done reading the stage
+    return true;
+  };
+  for (int it0 = 0; it0 < n_iters; it0 += kStages) {
+    if (!run_stages<0, kStages>(iteration, it0, n_iters)) break;
   }
 
   // ---------------- epilogue: reduce lanes, merge the warps of a head, write ----
@@ -1118,12 +1183,15 @@ int codes_map(CUtensorMap* m, const Plane& p, int row_bytes, int hpb, const Deco
   const int seg = hpb * row_bytes;  // the CTA's share of a token row
   if (seg >= 128) {
     if (seg % 128 || token_bytes % 128 || p.cs[1] < token_bytes || p.cs[0] < p.cs[1]) return 0;
-    const cuuint64_t dims[4] = {128, static_cast<cuuint64_t>(token_bytes / 128),
-                                static_cast<cuuint64_t>(a.block_size),
+    // dimension order (128 bytes, tokens of a page, 128-byte columns of a token row,
+    // blocks): one box brings ALL the CTA's columns of 16 tokens, column-major in
+    // shared memory ([column][token][128 bytes])
+    const cuuint64_t dims[4] = {128, static_cast<cuuint64_t>(a.block_size),
+                                static_cast<cuuint64_t>(token_bytes / 128),
                                 static_cast<cuuint64_t>(a.num_blocks)};
-    const cuuint64_t strides[3] = {128, static_cast<cuuint64_t>(p.cs[1]),
+    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(p.cs[1]), 128,
                                    static_cast<cuuint64_t>(p.cs[0])};
-    const cuuint32_t box[4] = {128, 1, 16, 1};
+    const cuuint32_t box[4] = {128, 16, static_cast<cuuint32_t>(seg / 128), 1};
     return encode(m, p.codes, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B) ? 1 : 0;
   }
   // narrow: the CTA holds every head and consecutive tokens are adjacent in memory
@@ -1248,11 +1316,11 @@ bool build_maps(const DecodeArgs& a, int hpb, TmaMaps* out) {
   return true;
 }
 
-template <int HD, int KMODE, int VMODE, bool SPLIT, bool TMA>
-int launch_inst(const DecodeArgs& a, const MmaParams& mp, const TmaMaps& tm, cudaStream_t st) {
+template <int HD, int KMODE, int VMODE, bool SPLIT, bool TMA, int HPBL>
+int launch_hpb(const DecodeArgs& a, const MmaParams& mp, const TmaMaps& tm, cudaStream_t st) {
   using G = Geo<HD, KMODE, TMA ? 0 : 16>;
   constexpr int kSmem = G::kSmemBytes + 1024;  // slack for the 1 KB alignment of the stages
-  auto kern = decode_mma_kernel<HD, KMODE, VMODE, SPLIT, TMA>;
+  auto kern = decode_mma_kernel<HD, KMODE, VMODE, SPLIT, TMA, HPBL>;
   static int configured_dev = -1;  // per instantiation; the attribute is per device function
   int dev = 0;
   cudaGetDevice(&dev);
@@ -1268,6 +1336,18 @@ int launch_inst(const DecodeArgs& a, const MmaParams& mp, const TmaMaps& tm, cud
   dim3 grid(a.n_splits, a.n_kv_heads / hpb, a.n_seqs);
   kern<<<grid, kThreads, kSmem, st>>>(a, mp, tm);
   return cudaGetLastError() == cudaSuccess ? KNLP_OK : KNLP_ERR_LAUNCH;
+}
+
+template <int HD, int KMODE, int VMODE, bool SPLIT, bool TMA>
+int launch_inst(const DecodeArgs& a, const MmaParams& mp, const TmaMaps& tm, cudaStream_t st) {
+  switch (mp.hpb_log2) {
+    case 0: return launch_hpb<HD, KMODE, VMODE, SPLIT, TMA, 0>(a, mp, tm, st);
+    case 1: return launch_hpb<HD, KMODE, VMODE, SPLIT, TMA, 1>(a, mp, tm, st);
+    case 2:
+      return launch_hpb<HD, KMODE, VMODE, SPLIT, TMA, (kWarpsLog < 2 ? kWarpsLog : 2)>(a, mp, tm, st);
+    default:
+      return launch_hpb<HD, KMODE, VMODE, SPLIT, TMA, (kWarpsLog < 3 ? kWarpsLog : 3)>(a, mp, tm, st);
+  }
 }
 
 template <int HD, int KMODE, int VMODE>
@@ -1334,7 +1414,7 @@ int launch_decode_mma(const DecodeArgs& a, bool allow_tma, cudaStream_t st) {
   if (a.block_size & (a.block_size - 1)) return 1;  // pages must be a power of two
   if (a.num_blocks > 0x7fffffff) return 1;
   MmaParams mp{};
-  mp.hpb_log2 = 3;
+  mp.hpb_log2 = kWarpsLog;
   while (mp.hpb_log2 > 0 && (a.n_kv_heads % (1 << mp.hpb_log2))) --mp.hpb_log2;
   const int hpb = 1 << mp.hpb_log2;
   const int kb = a.k.mode == KNLP_KV_INT8_G32 ? a.head_dim : a.head_dim / 2;
