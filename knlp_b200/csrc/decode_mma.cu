@@ -21,11 +21,13 @@
 // q heads of the kv group on the N side, which keeps the tile dense for GQA:
 //   scores  S_g[token, col] = sum_{d in group g} code[token, d] * q[col, d]
 //   output  O[d, col]      += sum_token code_v[token, d] * (p[token, col] * vscale[token, g(d)])
-// The codes enter the MMA as exact integers at no conversion cost: a nibble
-// masked in place inside an fp16 lane IS the fp16 subnormal code * 2^-24 (bits
-// 0-3) or code * 2^-20 (bits 4-7); the power of two is undone on the q side
-// (scores) or in the epilogue (output).  int8 codes are biased to unsigned and
-// byte-permuted into the low mantissa bits the same way.  Scale and zero-point
+// The codes enter the MMA as exact integers at no conversion cost: a nibble (or a
+// whole byte, even nibble + 16 x odd nibble) masked in place inside an fp16 lane IS
+// the fp16 subnormal value * 2^-24.  The mix of two nibbles in a byte is resolved by
+// the other operand (scores: the q slots are q_even - q_odd/16 and q_odd/16) or in the
+// epilogue (output: odd row = (mixed row - even row) / 16), the power of two likewise.
+// int8 codes are biased to unsigned and byte-permuted into the low mantissa bits the
+// same way.  Scale and zero-point
 // are applied per group outside the MMA:
 //   s = sum_g kscale_g * S_g + kzero_g * sum_{d in g} q[d]
 //   o += sum_token p * vzero_g   (accumulated on CUDA cores)
@@ -243,12 +245,31 @@ constexpr float kTwo24 = 16777216.0f;
 constexpr float kTwo20 = 1048576.0f;
 constexpr float kTwoM24 = 1.0f / 16777216.0f;
 
-// Eight nibbles of a 32-bit word -> four fp16x2 registers of fp16 SUBNORMALS:
-//   out[0] = (n0, n4) * 2^-24   out[1] = (n1, n5) * 2^-20
-//   out[2] = (n2, n6) * 2^-24   out[3] = (n3, n7) * 2^-20     n_i = bits [4i, 4i+4)
-// A half whose exponent field is zero has the value mantissa * 2^-24, so masking
-// a nibble in place is the whole conversion.
+// Eight nibbles of a 32-bit word -> four fp16x2 registers of fp16 SUBNORMALS
+// (n_i = bits [4i, 4i+4) of the word):
+//   out[0] = (n0,          n4         ) * 2^-24
+//   out[1] = (n0 + 16 n1,  n4 + 16 n5 ) * 2^-24      a whole byte left in place
+//   out[2] = (n2,          n6         ) * 2^-24
+//   out[3] = (n2 + 16 n3,  n6 + 16 n7 ) * 2^-24
+// A half whose exponent field is zero has the value mantissa * 2^-24, so masking in
+// place is the whole conversion (a byte still fits the 10-bit mantissa).  The odd
+// nibbles are never isolated - that would need a shift per word; instead the other
+// operand of the product absorbs the mix:
+//   n0 q0 + n1 q1 = n0 (q0 - q1/16) + (n0 + 16 n1) (q1/16)          (scores)
+// or the pure row is subtracted from the mixed one afterwards          (output rows).
 __device__ __forceinline__ void unpack_nibbles8(uint32_t w, uint32_t out[4]) {
+  out[0] = w & 0x000F000Fu;
+  out[1] = w & 0x00FF00FFu;
+  out[3] = __byte_perm(w, 0u, 0x4341);  // bytes 1 and 3 moved down, upper bytes cleared
+  out[2] = out[3] & 0x000F000Fu;
+}
+// The same with every nibble isolated (one more instruction per word):
+//   out[0] = (n0, n4) * 2^-24   out[1] = (n1, n5) * 2^-20
+//   out[2] = (n2, n6) * 2^-24   out[3] = (n3, n7) * 2^-20
+// Used for the scores when q is held as a single fp16 (5..8 q heads per kv head): there
+// the q slot of an odd nibble is just q_odd / 16 (exact), while the mixed form above
+// would round q_even - q_odd / 16 a second time.
+__device__ __forceinline__ void unpack_nibbles8_pure(uint32_t w, uint32_t out[4]) {
   const uint32_t w8 = w >> 8;
   out[0] = w & 0x000F000Fu;
   out[1] = w & 0x00F000F0u;
@@ -303,12 +324,13 @@ struct MmaParams {
 
 // Calls f(it0 + S, integral_constant<S>) for S = FIRST .. N-1 while it0 + S < n; stops
 // and returns false as soon as a call does.
-template <int S, int N, class F>
+// (CHECK = false: the caller guarantees it0 + N <= n.)
+template <int S, int N, bool CHECK = true, class F>
 __device__ __forceinline__ bool run_stages(F& f, int it0, int n) {
   if constexpr (S < N) {
-    if (it0 + S >= n) return true;
+    if (CHECK && it0 + S >= n) return true;
     if (!f(it0 + S, std::integral_constant<int, S>{})) return false;
-    return run_stages<S + 1, N>(f, it0, n);
+    return run_stages<S + 1, N, CHECK>(f, it0, n);
   } else {
     return true;
   }
@@ -403,14 +425,25 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
           d = 32 * g + 8 * ft + e;
         }
         float x = live ? load_elem_rt(a.q, qbase + d, a.q_dtype) : 0.0f;
+        float wgt = 1.0f;
+        if constexpr (!kInt8K) {
+          // The A operand holds, per byte, the even nibble alone and the whole byte
+          // (even + 16 * odd), see unpack_nibbles8: the even slot takes q_e - q_o / 16,
+          // the odd slot q_o / 16.  What multiplies the zero-point is then
+          // sum_e x_e + 17 sum_o x_o over the rounded slots.
+          // (With q as a single fp16 the nibbles are isolated instead and only the
+          // odd slot is scaled.)
+          if (e & 1) {
+            x *= 0.0625f;
+            if constexpr (SPLIT) wgt = 17.0f; else wgt = 16.0f;
+          } else if constexpr (SPLIT) {
+            const float xo = live ? load_elem_rt(a.q, qbase + d + 1, a.q_dtype) : 0.0f;
+            x -= xo * 0.0625f;
+          }
+        }
         __half h = __float2half_rn(x);
         if (lo_part) h = __float2half_rn(x - __half2float(h));
-        s += __half2float(h);
-        if constexpr (!kInt8K) {
-          // odd elements sit in bits 4-7 of their byte: their code arrives * 2^-20
-          // instead of * 2^-24, so the matching q is pre-divided by 16 (exact)
-          if (e & 1) h = __hmul(h, __float2half_rn(0.0625f));
-        }
+        s += wgt * __half2float(h);
         v[e] = h;
       }
       colsum[g] = s;
@@ -460,10 +493,20 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
   const int k_tt0 = tid >> k_lg, v_tt0 = tid >> v_lg;       // token of piece 0 in the stage
   const int k_dtt = kThreads >> k_lg, v_dtt = kThreads >> v_lg;  // token step between pieces
   const int k_j = tid & ((1 << k_lg) - 1), v_j = tid & ((1 << v_lg) - 1);
-  const uint8_t* k_src0 = a.k.codes + (hb * (G::KB << hpb_log2) + k_j * 16);
-  const uint8_t* v_src0 = a.v.codes + (hb * (G::VB << hpb_log2) + v_j * 16);
   const uint32_t kcs0 = static_cast<uint32_t>(a.k.cs[0]), kcs1 = static_cast<uint32_t>(a.k.cs[1]);
   const uint32_t vcs0 = static_cast<uint32_t>(a.v.cs[0]), vcs1 = static_cast<uint32_t>(a.v.cs[1]);
+  // k_pp[n] / v_pp[n]: this thread's n-th piece of a stage that starts at token 0 of
+  // block 0 (all other addresses are offsets from these)
+  const uint8_t* k_pp[kKPer];
+  const uint8_t* v_pp[kVPer];
+#pragma unroll
+  for (int n = 0; n < kKPer; ++n)
+    k_pp[n] = a.k.codes + (hb * (G::KB << hpb_log2) + k_j * 16) +
+              static_cast<uint32_t>(k_tt0 + n * k_dtt) * kcs1;
+#pragma unroll
+  for (int n = 0; n < kVPer; ++n)
+    v_pp[n] = a.v.codes + (hb * (G::VB << hpb_log2) + v_j * 16) +
+              static_cast<uint32_t>(v_tt0 + n * v_dtt) * vcs1;
   uint32_t k_dst[kKPer], v_dst[kVPer];
 #pragma unroll
   for (int n = 0; n < kKPer; ++n) {
@@ -492,10 +535,12 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
   const bool s_zero = (s_arr & 1) != 0;
   const __half* s_base = s_zero ? s_pl.zeros : s_pl.scales;
   const int64_t* s_st = s_zero ? s_pl.zs : s_pl.ss;
-  const uint8_t* s_src0 = reinterpret_cast<const uint8_t*>(s_base) +
-                          (hb * s_tb + (s_tb >= 16 ? s_byte % s_tb : 0));
   const uint32_t s_st0 = s_on ? static_cast<uint32_t>(s_st[0]) * 2 : 0;  // bytes
   const uint32_t s_st1 = s_on ? static_cast<uint32_t>(s_st[1]) * 2 : 0;
+  // the same for this thread's scale / zero piece (token s_tt of the stage)
+  const uint8_t* s_pp = reinterpret_cast<const uint8_t*>(s_base) +
+                        (hb * s_tb + (s_tb >= 16 ? s_byte % s_tb : 0)) +
+                        static_cast<uint32_t>(s_tt) * s_st1;
   // A warp later reads the 8 rows fr = 0..7 of ONE head in a single instruction; with
   // token rows of 32 or 64 bytes these would fall on the same banks (2- or 4-way
   // conflict).  So the 16-byte pieces of token row t are stored xor-permuted by the
@@ -539,8 +584,9 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
         const int tok = stage_tok0 + k_tt0 + n * k_dtt;
         const bool live = tok < end;
         const uint32_t blk = live ? page_id(slot, tok, page0) : 0u;
-        const uint8_t* src = k_src0 + (static_cast<uint64_t>(blk) * kcs0 +
-                                       static_cast<uint32_t>(tok & page_mask) * kcs1);
+        const int dt = (tok & page_mask) - (k_tt0 + n * k_dtt);  // token offset from k_pp[n]
+        const uint8_t* src = k_pp[n] + (static_cast<int64_t>(blk) * kcs0 +
+                                        static_cast<int64_t>(dt) * kcs1);
         cp_async16(k_dst[n] + stage_off, src, live ? 16 : 0);  // 0 -> zero fill
       }
     } else if (part == 1) {
@@ -549,16 +595,18 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
         const int tok = stage_tok0 + v_tt0 + n * v_dtt;
         const bool live = tok < end;
         const uint32_t blk = live ? page_id(slot, tok, page0) : 0u;
-        const uint8_t* src = v_src0 + (static_cast<uint64_t>(blk) * vcs0 +
-                                       static_cast<uint32_t>(tok & page_mask) * vcs1);
+        const int dt = (tok & page_mask) - (v_tt0 + n * v_dtt);
+        const uint8_t* src = v_pp[n] + (static_cast<int64_t>(blk) * vcs0 +
+                                        static_cast<int64_t>(dt) * vcs1);
         cp_async16(v_dst[n] + stage_off, src, live ? 16 : 0);
       }
     } else if (s_on) {
       const int tok = stage_tok0 + s_tt;
       const bool live = tok < end;
       const uint32_t blk = live ? page_id(slot, tok, page0) : 0u;
-      const uint8_t* src = s_src0 + (static_cast<uint64_t>(blk) * s_st0 +
-                                     static_cast<uint32_t>(tok & page_mask) * s_st1);
+      const int dt = (tok & page_mask) - s_tt;
+      const uint8_t* src = s_pp + (static_cast<int64_t>(blk) * s_st0 +
+                                   static_cast<int64_t>(dt) * s_st1);
       cp_async16(s_dst + stage_off, src, live ? 16 : 0);
     }
   };
@@ -566,8 +614,6 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
   // entirely before the end of the sequence.  One page lookup, one base address per
   // array, constant steps between a thread's pieces, no predicates.
   const bool one_page = TT <= (1 << mp.page_log2);
-  const uint32_t k_step = static_cast<uint32_t>(k_dtt) * kcs1;
-  const uint32_t v_step = static_cast<uint32_t>(v_dtt) * vcs1;
   auto issue_stage = [&](int it, auto stage_tag) {  // stage_tag: it % kStages as a constant
     constexpr int stage_off = decltype(stage_tag)::value * G::kStageBytes;
     const int stage_tok0 = start + it * TT;
@@ -575,21 +621,33 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
       const int raw = pg_tab[it & 7][0];
       const uint32_t blk = static_cast<uint32_t>(raw < 0 ? 0 : (raw > max_blk ? max_blk : raw));
       const uint32_t off_s = static_cast<uint32_t>(stage_tok0 & page_mask);
-      const uint8_t* kb = k_src0 + (static_cast<uint64_t>(blk) * kcs0 + (off_s + k_tt0) * kcs1);
+      const uint64_t ko = static_cast<uint64_t>(blk) * kcs0 + off_s * kcs1;
 #pragma unroll
-      for (int n = 0; n < kKPer; ++n) cp_async16_full_at<stage_off>(k_dst[n], kb + n * k_step);
-      const uint8_t* vb = v_src0 + (static_cast<uint64_t>(blk) * vcs0 + (off_s + v_tt0) * vcs1);
+      for (int n = 0; n < kKPer; ++n) cp_async16_full_at<stage_off>(k_dst[n], k_pp[n] + ko);
+      const uint64_t vo = static_cast<uint64_t>(blk) * vcs0 + off_s * vcs1;
 #pragma unroll
-      for (int n = 0; n < kVPer; ++n) cp_async16_full_at<stage_off>(v_dst[n], vb + n * v_step);
-      if (s_on) {
-        const uint8_t* sb = s_src0 + (static_cast<uint64_t>(blk) * s_st0 + (off_s + s_tt) * s_st1);
-        cp_async16_full_at<stage_off>(s_dst, sb);
-      }
+      for (int n = 0; n < kVPer; ++n) cp_async16_full_at<stage_off>(v_dst[n], v_pp[n] + vo);
+      if (s_on)
+        cp_async16_full_at<stage_off>(s_dst, s_pp + (static_cast<uint64_t>(blk) * s_st0 + off_s * s_st1));
       return;
     }
     issue_part(it, 0, stage_off);
     issue_part(it, 1, stage_off);
     issue_part(it, 2, stage_off);
+  };
+
+  // Steady state: block size == TT, so a whole stage is exactly one page and it lies
+  // before the end of the sequence.  A piece's address is then the thread's pointer into
+  // page 0 plus block id x block stride: one multiply-add and one copy per piece.
+  auto issue_steady = [&](int it, auto stage_tag) {
+    constexpr int stage_off = decltype(stage_tag)::value * G::kStageBytes;
+    const int raw = pg_tab[it & 7][0];
+    const uint64_t blk = static_cast<uint64_t>(raw < 0 ? 0 : (raw > max_blk ? max_blk : raw));
+#pragma unroll
+    for (int n = 0; n < kKPer; ++n) cp_async16_full_at<stage_off>(k_dst[n], k_pp[n] + blk * kcs0);
+#pragma unroll
+    for (int n = 0; n < kVPer; ++n) cp_async16_full_at<stage_off>(v_dst[n], v_pp[n] + blk * vcs0);
+    if (s_on) cp_async16_full_at<stage_off>(s_dst, s_pp + blk * s_st0);
   };
 
   const int n_iters = (end - start + TT - 1) / TT;
@@ -701,8 +759,8 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
   };
 
   // ---------------- accumulators ----------------
-  // oacc[g][j]: output rows d = 32g + 4fr + 2j (c0, c1; scaled 2^-24) and
-  // d = 32g + 4fr + 2j + 1 (c2, c3; scaled 2^-20), columns 2ft, 2ft+1
+  // oacc[g][j]: c0, c1 = output row d = 32g + 4fr + 2j; c2, c3 = that row + 16 x row
+  // d + 1 (the byte-wide operand); all scaled 2^-24; columns 2ft, 2ft+1
   float oacc[NG][2][4];
 #pragma unroll
   for (int g = 0; g < NG; ++g)
@@ -798,8 +856,12 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
   // compile-time constant, so every shared-memory offset of the body is an immediate;
   // the driver loop below steps through the stages kStages at a time.  Returns false
   // if a bounded barrier wait ran out.
-  auto iteration = [&](const int it, auto stage_tag) -> bool {
+  // steady_tag = true_type: the caller guarantees that this stage and the one refilled
+  // now are whole (and, for cp.async, that a stage is one page), which removes every
+  // end-of-sequence test from the body.
+  auto iteration = [&](const int it, auto stage_tag, auto steady_tag) -> bool {
     constexpr int kS = decltype(stage_tag)::value;
+    constexpr bool kSteady = decltype(steady_tag)::value;
     constexpr int kNextS = (kS + kStages - 1) % kStages;  // slot of stage it + kStages - 1
     if constexpr (TMA) {
       prefetch_pages(it + kStages);  // for the refill this warp may issue at the end
@@ -818,21 +880,27 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
     }
     if constexpr (!TMA) {
       const int nx = it + kStages - 1;
-      if (nx < n_iters) issue_stage(nx, std::integral_constant<int, kNextS>{});
+      if constexpr (kSteady) {
+        issue_steady(nx, std::integral_constant<int, kNextS>{});
+      } else {
+        if (nx < n_iters) issue_stage(nx, std::integral_constant<int, kNextS>{});
+      }
       cp_async_commit();
     }
 
     constexpr int stage_off = kS * G::kStageBytes;
     const uint8_t* st = smem + stage_off;
     const int tok0 = start + it * TT + w_tile * 16;  // first token of this warp's tile
-    if (tok0 >= end) {  // whole tile past the end (warp-uniform): nothing was loaded for it
-      if constexpr (TMA) release_slot(it, stage_tag);
-      return true;
+    if constexpr (!kSteady) {
+      if (tok0 >= end) {  // whole tile past the end (warp-uniform): nothing was loaded for it
+        if constexpr (TMA) release_slot(it, stage_tag);
+        return true;
+      }
     }
     // Rows past the end of a partial tile may hold whatever the page holds there (a TMA
     // box is always whole; a 16-byte scale piece can span two tokens), so their scales
     // are masked before use.
-    const bool partial = tok0 + 16 > end;
+    const bool partial = !kSteady && tok0 + 16 > end;
 
     // ---------------- scores ----------------
     float sacc[NG][4];
@@ -865,8 +933,13 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
           for (int s = 0; s < 2; ++s) {
             const int g = 2 * gp + s;
             uint32_t top[4], bot[4];
-            unpack_nibbles8(w[2 * s], top);
-            unpack_nibbles8(w[2 * s + 1], bot);
+            if constexpr (SPLIT) {
+              unpack_nibbles8(w[2 * s], top);
+              unpack_nibbles8(w[2 * s + 1], bot);
+            } else {
+              unpack_nibbles8_pure(w[2 * s], top);
+              unpack_nibbles8_pure(w[2 * s + 1], bot);
+            }
             mma16816(sacc[g], top[0], bot[0], top[1], bot[1], bq[g][0][0], bq[g][0][1]);
             mma16816(sacc[g], top[2], bot[2], top[3], bot[3], bq[g][1][0], bq[g][1][1]);
           }
@@ -1040,8 +1113,22 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
     if constexpr (TMA) release_slot(it, stage_tag);  // done reading the stage
     return true;
   };
-  for (int it0 = 0; it0 < n_iters; it0 += kStages) {
-    if (!run_stages<0, kStages>(iteration, it0, n_iters)) break;
+  {
+    const int n_full = (end - start) / TT;  // whole stages
+    int n_steady = n_full - (kStages - 1);  // iterations whose own and refilled stage are whole
+    if (!TMA && (1 << mp.page_log2) != TT) n_steady = 0;
+    n_steady = n_steady > 0 ? n_steady - n_steady % kStages : 0;
+    auto steady = [&](int it, auto stage_tag) -> bool {
+      return iteration(it, stage_tag, std::true_type{});
+    };
+    auto general = [&](int it, auto stage_tag) -> bool {
+      return iteration(it, stage_tag, std::false_type{});
+    };
+    bool ok = true;
+    int it0 = 0;
+    for (; ok && it0 < n_steady; it0 += kStages)
+      ok = run_stages<0, kStages, false>(steady, it0, n_steady);
+    for (; ok && it0 < n_iters; it0 += kStages) ok = run_stages<0, kStages>(general, it0, n_iters);
   }
 
   // ---------------- epilogue: reduce lanes, merge the warps of a head, write ----
@@ -1076,25 +1163,27 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
 #pragma unroll
     for (int g = 0; g < NG; ++g) {
       const int d0 = 32 * g + 4 * fr;
-      // undo the subnormal scaling: even elements 2^-24, odd elements 2^-20
+      // undo the 2^-24 of the subnormals; odd rows = (mixed - even) / 16
       if constexpr (SPLIT) {
         // head ft: hi column + lo column + zero term
         float4 v;
-        v.x = fmaf(oacc[g][0][0] + oacc[g][0][1], kTwo24, zacc[g][0]);
-        v.y = fmaf(oacc[g][0][2] + oacc[g][0][3], kTwo20, zacc[g][0]);
-        v.z = fmaf(oacc[g][1][0] + oacc[g][1][1], kTwo24, zacc[g][0]);
-        v.w = fmaf(oacc[g][1][2] + oacc[g][1][3], kTwo20, zacc[g][0]);
+        const float e0 = oacc[g][0][0] + oacc[g][0][1], m0 = oacc[g][0][2] + oacc[g][0][3];
+        const float e1 = oacc[g][1][0] + oacc[g][1][1], m1 = oacc[g][1][2] + oacc[g][1][3];
+        v.x = fmaf(e0, kTwo24, zacc[g][0]);
+        v.y = fmaf(m0 - e0, kTwo20, zacc[g][0]);
+        v.z = fmaf(e1, kTwo24, zacc[g][0]);
+        v.w = fmaf(m1 - e1, kTwo20, zacc[g][0]);
         *reinterpret_cast<float4*>(wo + ft * HD + d0) = v;
       } else {
         float4 v0, v1;
         v0.x = fmaf(oacc[g][0][0], kTwo24, zacc[g][0]);
-        v0.y = fmaf(oacc[g][0][2], kTwo20, zacc[g][0]);
+        v0.y = fmaf(oacc[g][0][2] - oacc[g][0][0], kTwo20, zacc[g][0]);
         v0.z = fmaf(oacc[g][1][0], kTwo24, zacc[g][0]);
-        v0.w = fmaf(oacc[g][1][2], kTwo20, zacc[g][0]);
+        v0.w = fmaf(oacc[g][1][2] - oacc[g][1][0], kTwo20, zacc[g][0]);
         v1.x = fmaf(oacc[g][0][1], kTwo24, zacc[g][NH - 1]);
-        v1.y = fmaf(oacc[g][0][3], kTwo20, zacc[g][NH - 1]);
+        v1.y = fmaf(oacc[g][0][3] - oacc[g][0][1], kTwo20, zacc[g][NH - 1]);
         v1.z = fmaf(oacc[g][1][1], kTwo24, zacc[g][NH - 1]);
-        v1.w = fmaf(oacc[g][1][3], kTwo20, zacc[g][NH - 1]);
+        v1.w = fmaf(oacc[g][1][3] - oacc[g][1][1], kTwo20, zacc[g][NH - 1]);
         *reinterpret_cast<float4*>(wo + (2 * ft) * HD + d0) = v0;
         *reinterpret_cast<float4*>(wo + (2 * ft + 1) * HD + d0) = v1;
       }
