@@ -106,12 +106,14 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------ CPU oracle leg
-def cpu_reference_sample(workload: str, scale: float, sample_tokens: int, repeats: int):
+def cpu_reference_sample(workload: str, scale: float, sample_tokens: int, repeats: int,
+                         inner: int = 1):
     """Time the CPU restatement of the reference path (oracle/kv_oracle.py) on a
     bounded sample: one sequence, all kv heads, ``sample_tokens`` tokens of the
     workload's distribution, quantized on the CPU by the oracle's own quantizer.
-    One worker thread per kv head.  Returns (bytes of the sample, [seconds of each
-    of the ``repeats`` runs], threads, description)."""
+    One worker thread per kv head; a timed run attends to the sample ``inner`` times
+    (``inner`` sequences of a batch).  Returns (bytes one run reads, [seconds of each of
+    the ``repeats`` runs], threads, description)."""
     import numpy as np
     from concurrent.futures import ThreadPoolExecutor
     from oracle import kv_oracle as O
@@ -146,11 +148,12 @@ def cpu_reference_sample(workload: str, scale: float, sample_tokens: int, repeat
     with ThreadPoolExecutor(max_workers=threads) as ex:
         for _ in range(repeats):
             t0 = time.perf_counter()
-            list(ex.map(one_head, range(hkv)))
+            for _ in range(inner):
+                list(ex.map(one_head, range(hkv)))
             secs.append(time.perf_counter() - t0)
-    nbytes = T * hkv * 160 + q.size * 4 * 2 + 4 * nb
-    desc = (f"1 sequence x {hkv} kv heads x {T} tokens of the workload's distribution "
-            f"(1/{max(1, round(32 * ctx * scale / T))} of a step), numpy oracle, {threads} threads")
+    nbytes = inner * (T * hkv * 160 + q.size * 4 * 2 + 4 * nb)
+    desc = (f"{inner} x (1 sequence x {hkv} kv heads x {T} tokens of the workload's distribution) "
+            f"= {inner * T / (32 * ctx * scale):.3g} of a step, numpy oracle, {threads} threads")
     return nbytes, secs, threads, desc
 
 
@@ -192,7 +195,10 @@ def run_ours(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        # a short collective timeout: a rank that fell out of step ends the run in
+        # minutes instead of holding the GPUs for NCCL's default ten
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
 
     def barrier():
         if world > 1:
@@ -268,10 +274,16 @@ def run_ours(args):
     barrier()
     total_ms = (sum(a.elapsed_time(b) for a, b in sev) if need_flush else e0.elapsed_time(e1))
     kern_ms = sum(a.elapsed_time(b) for a, b in ev) / K
-    # keep the sampler running for at least ~0.6 s of load so it sees the clocks
-    t_end = time.time() + (0.0 if args.profile else 1.0)
-    while time.time() < t_end:
-        step(w.seq_lens, w.max_seq_len)
+    # keep the load up for about a second more so the sampler sees the clocks.  The
+    # number of extra steps is agreed between the ranks (a context shard has a collective
+    # in every step, so every rank must run the same count).
+    if not args.profile:
+        extra = torch.tensor([min(20000, max(1, int(1000.0 / max(total_ms / K, 1e-3))))],
+                             dtype=torch.int64, device=dev)
+        if world > 1:
+            dist.all_reduce(extra, op=dist.ReduceOp.MAX)
+        for _ in range(int(extra.item())):
+            step(w.seq_lens, w.max_seq_len)
     torch.cuda.synchronize()
     clocks = sampler.stop() if rank == 0 else None
     if args.profile:
@@ -374,7 +386,7 @@ def run_ours(args):
             "gpu_launches": (3 if ctx_mode else 2) * K,
         }
         if world == 1 and not args.no_cpu:
-            nbytes, secs, threads, desc = cpu_reference_sample(args.workload, args.scale, 32768, 4)
+            nbytes, secs, threads, desc = cpu_reference_sample(args.workload, args.scale, 65536, 4, inner=8)
             best = min(secs[1:])
             line["cpu_baseline"] = {"value": nbytes / best / 1e12, "unit": UNIT, "cores": threads,
                                     "kind": "port", "sample": desc + ", best of 3 after 1 warm-up",
