@@ -172,6 +172,27 @@ int knlp_b200_combine(const float* part_m, const float* part_l, const float* par
                       int n_rows, int head_dim, void* stream);
 
 /*
+ * Plugin-level simulated quantizers.  Replace the tensor expressions of
+ * backends/quant.py: quantize_int8_symmetric (:23-35; group = dim, bits = 8),
+ * quantize_int4_block (:43-72; group = block size, bits = 4, one code per int8, the
+ * last block of a row may be partial), dequantize_int8_symmetric (:38-40) and
+ * dequantize_int4_block (:75-86).
+ *   x       [n_rows, dim] of dtype, rows contiguous
+ *   q       int8 [n_rows, dim]
+ *   scale   [n_rows, ceil(dim / group)] of the SAME dtype as x (as the reference returns)
+ *   out     float [n_rows, dim] = q * scale
+ * Arithmetic is carried out in x's dtype as the reference does (amax floor 1e-8, scale
+ * and quotient each rounded to that dtype), integer rounding is half-to-even, so codes
+ * and scales are bit-identical to the reference's.  A row that is all zero in fp16
+ * (where the floor rounds to 0) is 0 / 0 in the reference; here its codes are the range
+ * minimum and its scale 0.
+ */
+int knlp_b200_plugin_quantize(const void* x, int dtype, int64_t n_rows, int dim, int group,
+                              int bits, int8_t* q, void* scale, void* stream);
+int knlp_b200_plugin_dequantize(const int8_t* q, const void* scale, int scale_dtype,
+                                int64_t n_rows, int dim, int group, float* out, void* stream);
+
+/*
  * Decode attention straight to the output, with NO device allocation by anyone.
  * It has no counterpart in the reference.  It exists for hosts that cannot hand
  * knlp_b200_decode_splitk a workspace: an engine that gave all device memory to its

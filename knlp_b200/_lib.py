@@ -30,6 +30,8 @@ SYMBOLS = (
     "knlp_b200_decode_splitk",
     "knlp_b200_combine",
     "knlp_b200_decode_noalloc",
+    "knlp_b200_plugin_quantize",
+    "knlp_b200_plugin_dequantize",
 )
 
 
@@ -95,6 +97,13 @@ def load() -> C.CDLL:
         C.c_void_p, C.c_int, I64P, PL, PL, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
         C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
         C.c_void_p, C.c_int, C.c_int64, C.c_void_p]
+    lib.knlp_b200_plugin_quantize.restype = C.c_int
+    lib.knlp_b200_plugin_quantize.argtypes = [
+        C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
+        C.c_void_p]
+    lib.knlp_b200_plugin_dequantize.restype = C.c_int
+    lib.knlp_b200_plugin_dequantize.argtypes = [
+        C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
     if lib.knlp_b200_abi_version() != ABI_VERSION:
         raise RuntimeError("libknlp_b200.so ABI version mismatch; rebuild it")
     _lib = lib

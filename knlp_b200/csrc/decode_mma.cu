@@ -95,23 +95,10 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int sr
                "r"(src_bytes)
                : "memory");
 }
-__device__ __forceinline__ void cp_async16_full(uint32_t dst, const void* src) {
-  asm volatile("cp.async." KNLP_CP_MODE ".shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
-}
 template <int OFF>  // destination = dst + OFF, the offset folded into the address operand
 __device__ __forceinline__ void cp_async16_full_at(uint32_t dst, const void* src) {
   asm volatile("cp.async." KNLP_CP_MODE ".shared.global [%0+%2], [%1], 16;\n" ::"r"(dst), "l"(src),
                "n"(OFF)
-               : "memory");
-}
-__device__ __forceinline__ void cp_async8(uint32_t dst, const void* src, int src_bytes) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;\n" ::"r"(dst), "l"(src),
-               "r"(src_bytes)
-               : "memory");
-}
-__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src, int src_bytes) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(dst), "l"(src),
-               "r"(src_bytes)
                : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() {
@@ -122,17 +109,8 @@ __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
 }
 
-__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t r[4]) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(addr));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t r[4]) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(addr));
-}
-// the same with a compile-time byte offset folded into the address operand
+// ldmatrix x4 (and its transposing form) with a compile-time byte offset folded into the
+// address operand
 template <int OFF>
 __device__ __forceinline__ void ldmatrix_x4_at(uint32_t addr, uint32_t r[4]) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4+%5];\n"
@@ -168,9 +146,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // ---- mbarrier + TMA (cp.async.bulk.tensor) primitives, CTA scope, no multicast ----
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes)
@@ -495,18 +470,19 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
   const int k_j = tid & ((1 << k_lg) - 1), v_j = tid & ((1 << v_lg) - 1);
   const uint32_t kcs0 = static_cast<uint32_t>(a.k.cs[0]), kcs1 = static_cast<uint32_t>(a.k.cs[1]);
   const uint32_t vcs0 = static_cast<uint32_t>(a.v.cs[0]), vcs1 = static_cast<uint32_t>(a.v.cs[1]);
-  // k_pp[n] / v_pp[n]: this thread's n-th piece of a stage that starts at token 0 of
-  // block 0 (all other addresses are offsets from these)
+  // k_pp[n] / v_pp[n]: this thread's n-th piece (token tt of the stage) in block 0 of
+  // a cache with 16-token blocks, i.e. at token tt % 16 of the block; every other
+  // address is an offset from these
   const uint8_t* k_pp[kKPer];
   const uint8_t* v_pp[kVPer];
 #pragma unroll
   for (int n = 0; n < kKPer; ++n)
     k_pp[n] = a.k.codes + (hb * (G::KB << hpb_log2) + k_j * 16) +
-              static_cast<uint32_t>(k_tt0 + n * k_dtt) * kcs1;
+              static_cast<uint32_t>((k_tt0 + n * k_dtt) & 15) * kcs1;
 #pragma unroll
   for (int n = 0; n < kVPer; ++n)
     v_pp[n] = a.v.codes + (hb * (G::VB << hpb_log2) + v_j * 16) +
-              static_cast<uint32_t>(v_tt0 + n * v_dtt) * vcs1;
+              static_cast<uint32_t>((v_tt0 + n * v_dtt) & 15) * vcs1;
   uint32_t k_dst[kKPer], v_dst[kVPer];
 #pragma unroll
   for (int n = 0; n < kKPer; ++n) {
@@ -540,7 +516,7 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
   // the same for this thread's scale / zero piece (token s_tt of the stage)
   const uint8_t* s_pp = reinterpret_cast<const uint8_t*>(s_base) +
                         (hb * s_tb + (s_tb >= 16 ? s_byte % s_tb : 0)) +
-                        static_cast<uint32_t>(s_tt) * s_st1;
+                        static_cast<uint32_t>(s_tt & 15) * s_st1;
   // A warp later reads the 8 rows fr = 0..7 of ONE head in a single instruction; with
   // token rows of 32 or 64 bytes these would fall on the same banks (2- or 4-way
   // conflict).  So the 16-byte pieces of token row t are stored xor-permuted by the
@@ -584,7 +560,7 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
         const int tok = stage_tok0 + k_tt0 + n * k_dtt;
         const bool live = tok < end;
         const uint32_t blk = live ? page_id(slot, tok, page0) : 0u;
-        const int dt = (tok & page_mask) - (k_tt0 + n * k_dtt);  // token offset from k_pp[n]
+        const int dt = (tok & page_mask) - ((k_tt0 + n * k_dtt) & 15);  // tokens from k_pp[n]
         const uint8_t* src = k_pp[n] + (static_cast<int64_t>(blk) * kcs0 +
                                         static_cast<int64_t>(dt) * kcs1);
         cp_async16(k_dst[n] + stage_off, src, live ? 16 : 0);  // 0 -> zero fill
@@ -595,7 +571,7 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
         const int tok = stage_tok0 + v_tt0 + n * v_dtt;
         const bool live = tok < end;
         const uint32_t blk = live ? page_id(slot, tok, page0) : 0u;
-        const int dt = (tok & page_mask) - (v_tt0 + n * v_dtt);
+        const int dt = (tok & page_mask) - ((v_tt0 + n * v_dtt) & 15);
         const uint8_t* src = v_pp[n] + (static_cast<int64_t>(blk) * vcs0 +
                                         static_cast<int64_t>(dt) * vcs1);
         cp_async16(v_dst[n] + stage_off, src, live ? 16 : 0);
@@ -604,7 +580,7 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
       const int tok = stage_tok0 + s_tt;
       const bool live = tok < end;
       const uint32_t blk = live ? page_id(slot, tok, page0) : 0u;
-      const int dt = (tok & page_mask) - s_tt;
+      const int dt = (tok & page_mask) - (s_tt & 15);
       const uint8_t* src = s_pp + (static_cast<int64_t>(blk) * s_st0 +
                                    static_cast<int64_t>(dt) * s_st1);
       cp_async16(s_dst + stage_off, src, live ? 16 : 0);
@@ -623,12 +599,18 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
       const uint32_t off_s = static_cast<uint32_t>(stage_tok0 & page_mask);
       const uint64_t ko = static_cast<uint64_t>(blk) * kcs0 + off_s * kcs1;
 #pragma unroll
-      for (int n = 0; n < kKPer; ++n) cp_async16_full_at<stage_off>(k_dst[n], k_pp[n] + ko);
+      for (int n = 0; n < kKPer; ++n)
+        cp_async16_full_at<stage_off>(
+            k_dst[n], k_pp[n] + (ko + (TT > 16 ? ((k_tt0 + n * k_dtt) & ~15u) * kcs1 : 0u)));
       const uint64_t vo = static_cast<uint64_t>(blk) * vcs0 + off_s * vcs1;
 #pragma unroll
-      for (int n = 0; n < kVPer; ++n) cp_async16_full_at<stage_off>(v_dst[n], v_pp[n] + vo);
+      for (int n = 0; n < kVPer; ++n)
+        cp_async16_full_at<stage_off>(
+            v_dst[n], v_pp[n] + (vo + (TT > 16 ? ((v_tt0 + n * v_dtt) & ~15u) * vcs1 : 0u)));
       if (s_on)
-        cp_async16_full_at<stage_off>(s_dst, s_pp + (static_cast<uint64_t>(blk) * s_st0 + off_s * s_st1));
+        cp_async16_full_at<stage_off>(
+            s_dst, s_pp + (static_cast<uint64_t>(blk) * s_st0 +
+                           (off_s + (TT > 16 ? (s_tt & ~15u) : 0u)) * s_st1));
       return;
     }
     issue_part(it, 0, stage_off);
@@ -636,18 +618,31 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
     issue_part(it, 2, stage_off);
   };
 
-  // Steady state: block size == TT, so a whole stage is exactly one page and it lies
-  // before the end of the sequence.  A piece's address is then the thread's pointer into
-  // page 0 plus block id x block stride: one multiply-add and one copy per piece.
+  // Steady state: 16-token blocks, and the stage lies before the end of the sequence.
+  // Each of its 16-token tiles is then exactly one block, and a piece's address is the
+  // thread's pointer into block 0 plus block id x block stride: one page-table read, one
+  // multiply-add and one copy per piece, no predicates.
+  auto steady_blk = [&](int it, int tt) -> uint64_t {
+    const int raw = pg_tab[it & 7][TT > 16 ? (tt >> 4) : 0];
+    return static_cast<uint64_t>(raw < 0 ? 0 : (raw > max_blk ? max_blk : raw));
+  };
   auto issue_steady = [&](int it, auto stage_tag) {
     constexpr int stage_off = decltype(stage_tag)::value * G::kStageBytes;
-    const int raw = pg_tab[it & 7][0];
-    const uint64_t blk = static_cast<uint64_t>(raw < 0 ? 0 : (raw > max_blk ? max_blk : raw));
+    // all page ids first: the copies below are memory barriers to the compiler, a
+    // lookup placed between them would be repeated
+    uint64_t kb[kKPer], vb[kVPer];
 #pragma unroll
-    for (int n = 0; n < kKPer; ++n) cp_async16_full_at<stage_off>(k_dst[n], k_pp[n] + blk * kcs0);
+    for (int n = 0; n < kKPer; ++n)
+      kb[n] = (TT > 16 || n == 0) ? steady_blk(it, k_tt0 + n * k_dtt) : kb[0];
 #pragma unroll
-    for (int n = 0; n < kVPer; ++n) cp_async16_full_at<stage_off>(v_dst[n], v_pp[n] + blk * vcs0);
-    if (s_on) cp_async16_full_at<stage_off>(s_dst, s_pp + blk * s_st0);
+    for (int n = 0; n < kVPer; ++n)
+      vb[n] = TT > 16 ? steady_blk(it, v_tt0 + n * v_dtt) : kb[0];
+    const uint64_t sb = TT > 16 ? steady_blk(it, s_tt) : kb[0];
+#pragma unroll
+    for (int n = 0; n < kKPer; ++n) cp_async16_full_at<stage_off>(k_dst[n], k_pp[n] + kb[n] * kcs0);
+#pragma unroll
+    for (int n = 0; n < kVPer; ++n) cp_async16_full_at<stage_off>(v_dst[n], v_pp[n] + vb[n] * vcs0);
+    if (s_on) cp_async16_full_at<stage_off>(s_dst, s_pp + sb * s_st0);
   };
 
   const int n_iters = (end - start + TT - 1) / TT;
@@ -820,7 +815,6 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
   // ldmatrix source row of this lane: row (lane & 7) + 8 * ((lane >> 3) & 1), piece + (lane >> 4)
   const int lm_row = (lane & 7) + ((lane >> 3) & 1) * 8;
   const int lm_q = lane >> 4;
-  const int Rbase = warp * 16;
   const uint32_t k_lm0 = smem_base + G::kOffK + warp * G::kTileK + lm_row * G::KB;
   const uint32_t v_lm0 = smem_base + G::kOffV + warp * G::kTileV + lm_row * G::VB;
   // piece offsets of the ldmatrix calls (piece index xor row swizzle), fixed per thread
@@ -862,7 +856,7 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
   auto iteration = [&](const int it, auto stage_tag, auto steady_tag) -> bool {
     constexpr int kS = decltype(stage_tag)::value;
     constexpr bool kSteady = decltype(steady_tag)::value;
-    constexpr int kNextS = (kS + kStages - 1) % kStages;  // slot of stage it + kStages - 1
+    [[maybe_unused]] constexpr int kNextS = (kS + kStages - 1) % kStages;  // slot refilled now
     if constexpr (TMA) {
       prefetch_pages(it + kStages);  // for the refill this warp may issue at the end
       if (!mbar_wait(bar0 + kS * 8, static_cast<uint32_t>(it / kStages) & 1u)) lost = true;
@@ -1116,7 +1110,7 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
   {
     const int n_full = (end - start) / TT;  // whole stages
     int n_steady = n_full - (kStages - 1);  // iterations whose own and refilled stage are whole
-    if (!TMA && (1 << mp.page_log2) != TT) n_steady = 0;
+    if (!TMA && mp.page_log2 != 4) n_steady = 0;  // the steady copies assume 16-token blocks
     n_steady = n_steady > 0 ? n_steady - n_steady % kStages : 0;
     auto steady = [&](int it, auto stage_tag) -> bool {
       return iteration(it, stage_tag, std::true_type{});

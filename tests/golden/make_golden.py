@@ -160,11 +160,50 @@ def gen_decode_cases(m, out):
         print("decode", name, "done", flush=True)
 
 
+def gen_plugin_cases(out):
+    """Plugin-level simulated quantizers (backends/quant.py:23-86), run as they are on
+    CPU tensors of each dtype.  Values are stored as fp32 views (exact)."""
+    sys.path.insert(0, REF)
+    from backends import quant as Q  # noqa: E402  (the reference module itself)
+
+    rec = {}
+    for dt_name, dt in (("f32", torch.float32), ("f16", torch.float16), ("bf16", torch.bfloat16)):
+        for D in (64, 80):  # 80: the int4 block quantizer pads the last block
+            g = torch.Generator().manual_seed(4000 + D)
+            x = torch.randn(2, 3, 13, D, generator=g)
+            x[0, 0, 1] *= 50.0          # a large row
+            x[0, 1, 2] *= 1e-3          # a small row
+            x[1, 2, 5, :7] = 0.5        # ties after scaling are possible here
+            if dt == torch.float32:
+                x[1, 0, 0] = 0.0        # all-zero row: the 1e-8 floor (fp32 only: in
+                                        # fp16 the floor rounds to 0 and the row is 0/0)
+            x = x.to(dt)
+            q8, s8 = Q.quantize_int8_symmetric(x)
+            d8 = Q.dequantize_int8_symmetric(q8, s8)
+            q4, s4 = Q.quantize_int4_block(x, 32)
+            d4 = Q.dequantize_int4_block(q4, s4, 32)
+            key = f"{dt_name}_d{D}"
+            rec[key + "_x"] = x.float().numpy()
+            rec[key + "_q8"] = q8.numpy()
+            rec[key + "_s8"] = s8.float().numpy()
+            rec[key + "_d8"] = d8.float().numpy()
+            rec[key + "_q4"] = q4.numpy()
+            rec[key + "_s4"] = s4.float().numpy()
+            rec[key + "_d4"] = d4.float().numpy()
+            assert s8.dtype == dt and s4.dtype == dt and d8.dtype == torch.float32
+    out["plugin_quant"] = rec
+    print("plugin quantizers done", flush=True)
+
+
 def main():
-    m = load_reference()
     out = {}
-    gen_write_cases(m, out)
-    gen_decode_cases(m, out)
+    if "--only-plugin" in sys.argv:
+        gen_plugin_cases(out)
+    else:
+        m = load_reference()
+        gen_write_cases(m, out)
+        gen_decode_cases(m, out)
+        gen_plugin_cases(out)
     for name, rec in out.items():
         np.savez_compressed(os.path.join(HERE, name + ".npz"), **rec)
         print("saved", name)

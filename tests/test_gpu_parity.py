@@ -292,6 +292,21 @@ def test_decode_edge_lengths(length, cuda_device):
             assert np.all(out[0] == 0)
 
 
+@pytest.mark.parametrize("n_kv,n_rep", [(1, 4), (2, 4), (3, 2), (4, 8), (8, 1), (12, 1)])
+def test_decode_kv_heads_per_cta(n_kv, n_rep, cuda_device):
+    """1, 2 or 4 kv heads per CTA (a stage is then 4, 2 or 1 sixteen-token blocks), long
+    enough that most stages go through the loop without end-of-sequence tests, ragged
+    so that the last stages do not; shuffled pages."""
+    from knlp_b200 import workloads
+    w = workloads.build("few_heads", n_seqs=3, n_q_heads=n_kv * n_rep, n_kv_heads=n_kv,
+                        head_dim=128, seq_lens=[2500, 1031, 64], seed=500 + n_kv,
+                        device=cuda_device, shuffle_pages=True)
+    ref = _workload_oracle(w)
+    for kw in (dict(), dict(n_splits=1), dict(n_splits=3), dict(force_generic="tma")):
+        out = w.decode(out_dtype=torch.float32, **kw).cpu().numpy()
+        assert_close(out, ref, f"kv heads {n_kv} x rep {n_rep} {kw}")
+
+
 def test_head_major_cache_view_goes_generic(cuda_device):
     """A [block, head, token, d/2] cache viewed as [block, token, head, d/2] has a
     16-byte-aligned but permuted layout; both kernels must address it."""
