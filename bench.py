@@ -230,9 +230,19 @@ def run_ours(args):
     vp = _plane(w.value_cache, w.v_scales, w.v_zeros if vasym else None, _int4_mode(vasym, w.v_zeros))
     nblocks = w.key_cache.shape[0]
 
+    two_launches = (not args.single_launch) or ctx_mode
+
     def step(seq_lens, max_len, rec=None):
         if rec is not None:
             rec[0].record()
+        if not two_launches:
+            # one launch: split-context decode whose last CTA per row group merges the splits
+            o = ops.decode_attention(w.query, kp, vp, nblocks, w.block_table, seq_lens,
+                                     w.n_kv_heads, d, PAGE, max_seq_len=max_len,
+                                     n_splits=n_splits)
+            if rec is not None:
+                rec[1].record()
+            return o
         pm, pl, po = ops.decode_partials(w.query, kp, vp, nblocks, w.block_table, seq_lens,
                                          w.n_kv_heads, d, PAGE, max_seq_len=max_len,
                                          n_splits=n_splits)
@@ -319,12 +329,16 @@ def run_ours(args):
         ln = lens1_h.to(dev, non_blocking=True)
         sl = slots_h.to(dev, non_blocking=True)
         workloads.append_tokens(caches, kn, vn, sl, w.k_mode, w.v_mode)
-        pm, pl, po = ops.decode_partials(q, kp, vp, nblocks, bt, ln, w.n_kv_heads, d, PAGE,
-                                         max_seq_len=w.max_seq_len + 1, n_splits=n_splits)
-        if ctx_mode:
-            o = shardlib.context_sharded_decode((pm, pl, po), out_dtype=w.query.dtype)
+        if not two_launches:
+            o = ops.decode_attention(q, kp, vp, nblocks, bt, ln, w.n_kv_heads, d, PAGE,
+                                     max_seq_len=w.max_seq_len + 1, n_splits=n_splits)
         else:
-            o = ops.combine_partials(pm, pl, po, out_dtype=w.query.dtype)
+            pm, pl, po = ops.decode_partials(q, kp, vp, nblocks, bt, ln, w.n_kv_heads, d, PAGE,
+                                             max_seq_len=w.max_seq_len + 1, n_splits=n_splits)
+            if ctx_mode:
+                o = shardlib.context_sharded_decode((pm, pl, po), out_dtype=w.query.dtype)
+            else:
+                o = ops.combine_partials(pm, pl, po, out_dtype=w.query.dtype)
         out_h.copy_(o, non_blocking=True)
 
     for _ in range(3):
@@ -383,7 +397,9 @@ def run_ours(args):
             "e2e": {"value": alg_total / (e2e_ms / K / 1e3) / 1e12, "unit": UNIT,
                     "ms_per_step": e2e_ms / K, "h2d_bytes_per_step": int(h2d_total),
                     "d2h_bytes_per_step": int(d2h_total)},
-            "gpu_launches": (3 if ctx_mode else 2) * K,
+            # kernels of this library in the timed region per step: decode + combine (a
+            # context shard merges twice; --single-launch merges inside the decode kernel)
+            "gpu_launches": (3 if ctx_mode else 2 if two_launches else 1) * K,
         }
         if world == 1 and not args.no_cpu:
             nbytes, secs, threads, desc = cpu_reference_sample(args.workload, args.scale, 65536, 4, inner=8)
@@ -406,6 +422,9 @@ def main():
     ap.add_argument("--scale", type=float, default=1.0)
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--single-launch", action="store_true",
+                    help="merge the splits inside the decode kernel (its last CTA per row group) "
+                         "instead of the separate combine kernel; measured slightly slower")
     ap.add_argument("--shard", default="heads", choices=["heads", "context"],
                     help="how N > 1 GPUs split the work (default: kv heads, no exchange)")
     ap.add_argument("--profile", action="store_true",

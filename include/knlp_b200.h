@@ -152,6 +152,31 @@ int knlp_b200_decode_splitk(const void* query, int q_dtype, const int64_t q_stri
                             unsigned flags, void* stream);
 
 /*
+ * Decode attention in ONE launch: knlp_b200_decode_splitk whose CTAs also merge the
+ * splits (the CTA that finishes a sequence's group of kv heads last does it), i.e. the
+ * whole of fused_int4_decode / kint8_vint4_decode (reference :901-979, :1496-1554).
+ * Arguments as knlp_b200_decode_splitk (the partials workspace is still needed; part_o
+ * must be 16-byte aligned here), plus
+ *   counters     int32 [n_seqs * n_kv_heads] (an upper bound of what is used: one per
+ *                sequence and group of kv heads that a CTA covers), all ZERO on entry; the kernel
+ *                leaves them zero, so one buffer zeroed once serves every later call on
+ *                the same stream (calls that may overlap need separate buffers)
+ *   out          [n_seqs * n_q_heads, head_dim] of out_dtype, row stride out_row_stride
+ *                elements: normalised attention output, 0 for sequences without tokens
+ * Layouts that only the stride-generic kernel can address are finished with the
+ * combine kernel instead; the result is the same.
+ */
+int knlp_b200_decode_attention(const void* query, int q_dtype, const int64_t q_stride[2],
+                               const knlp_kv_plane* k_plane, const knlp_kv_plane* v_plane,
+                               const int32_t* block_table, int64_t bt_stride,
+                               const int32_t* seq_lens, int64_t num_blocks,
+                               int n_seqs, int n_q_heads, int n_kv_heads, int head_dim,
+                               int block_size, int n_splits, int max_seq_len,
+                               float* part_m, float* part_l, float* part_o, int32_t* counters,
+                               void* out, int out_dtype, int64_t out_row_stride,
+                               unsigned flags, void* stream);
+
+/*
  * Merge n_parts partials per (sequence, q head) row.  No counterpart function
  * in the reference: the algebra is its in-loop online-softmax recurrence
  * (:808-815, :883-887) applied across splits.

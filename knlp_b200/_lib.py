@@ -28,6 +28,7 @@ SYMBOLS = (
     "knlp_b200_quant_append",
     "knlp_b200_decode_plan",
     "knlp_b200_decode_splitk",
+    "knlp_b200_decode_attention",
     "knlp_b200_combine",
     "knlp_b200_decode_noalloc",
     "knlp_b200_plugin_quantize",
@@ -87,6 +88,12 @@ def load() -> C.CDLL:
         C.c_void_p, C.c_int, I64P, PL, PL, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
         C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
         C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint, C.c_void_p]
+    lib.knlp_b200_decode_attention.restype = C.c_int
+    lib.knlp_b200_decode_attention.argtypes = [
+        C.c_void_p, C.c_int, I64P, PL, PL, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
+        C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+        C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64,
+        C.c_uint, C.c_void_p]
     lib.knlp_b200_combine.restype = C.c_int
     lib.knlp_b200_combine.argtypes = [
         C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_int64, C.c_int64,

@@ -143,13 +143,18 @@ int knlp_b200_decode_plan(int n_seqs, int n_q_heads, int n_kv_heads, int head_di
   return KNLP_OK;
 }
 
-int knlp_b200_decode_splitk(const void* query, int q_dtype, const int64_t q_stride[2],
-                            const knlp_kv_plane* k_plane, const knlp_kv_plane* v_plane,
-                            const int32_t* block_table, int64_t bt_stride,
-                            const int32_t* seq_lens, int64_t num_blocks, int n_seqs,
-                            int n_q_heads, int n_kv_heads, int head_dim, int block_size,
-                            int n_splits, int max_seq_len, float* part_m, float* part_l,
-                            float* part_o, unsigned flags, void* stream) {
+}  // extern "C"
+
+namespace {
+
+// Shared body of the two decode entry points.  out == nullptr: partials only.
+int decode_common(const void* query, int q_dtype, const int64_t q_stride[2],
+                  const knlp_kv_plane* k_plane, const knlp_kv_plane* v_plane,
+                  const int32_t* block_table, int64_t bt_stride, const int32_t* seq_lens,
+                  int64_t num_blocks, int n_seqs, int n_q_heads, int n_kv_heads, int head_dim,
+                  int block_size, int n_splits, int max_seq_len, float* part_m, float* part_l,
+                  float* part_o, int* counters, void* out, int out_dtype,
+                  int64_t out_row_stride, unsigned flags, void* stream) {
   if (!query || !q_stride || !block_table || !seq_lens || !part_m || !part_l || !part_o)
     return KNLP_ERR_NULL;
   if (!dtype_ok(q_dtype)) return KNLP_ERR_DTYPE;
@@ -186,12 +191,58 @@ int knlp_b200_decode_splitk(const void* query, int q_dtype, const int64_t q_stri
   a.part_m = part_m;
   a.part_l = part_l;
   a.part_o = part_o;
+  // the kernel merges the splits itself only while they are few (kFuseMaxSplits)
+  const bool fuse = out != nullptr && n_splits <= kFuseMaxSplits;
+  a.out = fuse ? out : nullptr;
+  a.out_dtype = out_dtype;
+  a.out_row_stride = out_row_stride;
+  a.counters = counters;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  rc = 1;
   if (!(flags & KNLP_DECODE_FORCE_GENERIC)) {
     rc = launch_decode_mma(a, (flags & KNLP_DECODE_USE_TMA) != 0, st);
-    if (rc <= 0) return rc;  // launched, or failed for good
+    if (rc < 0 || (rc == 0 && (fuse || !out))) return rc;  // done, or failed for good
   }
-  return launch_decode_generic(a, st);
+  if (rc == 1) rc = launch_decode_generic(a, st);
+  if (rc != KNLP_OK || !out) return rc;
+  // many splits, or the stride-generic kernel: merge with the combine kernel
+  return launch_combine(part_m, part_l, part_o, n_splits, n_splits, 1,
+                        static_cast<int64_t>(n_splits) * head_dim, head_dim, out, out_dtype,
+                        out_row_stride, nullptr, nullptr, 0, n_seqs * n_q_heads, head_dim, st);
+}
+
+}  // namespace
+
+extern "C" {
+
+int knlp_b200_decode_splitk(const void* query, int q_dtype, const int64_t q_stride[2],
+                            const knlp_kv_plane* k_plane, const knlp_kv_plane* v_plane,
+                            const int32_t* block_table, int64_t bt_stride,
+                            const int32_t* seq_lens, int64_t num_blocks, int n_seqs,
+                            int n_q_heads, int n_kv_heads, int head_dim, int block_size,
+                            int n_splits, int max_seq_len, float* part_m, float* part_l,
+                            float* part_o, unsigned flags, void* stream) {
+  return decode_common(query, q_dtype, q_stride, k_plane, v_plane, block_table, bt_stride,
+                       seq_lens, num_blocks, n_seqs, n_q_heads, n_kv_heads, head_dim, block_size,
+                       n_splits, max_seq_len, part_m, part_l, part_o, nullptr, nullptr, KNLP_F32,
+                       0, flags, stream);
+}
+
+int knlp_b200_decode_attention(const void* query, int q_dtype, const int64_t q_stride[2],
+                               const knlp_kv_plane* k_plane, const knlp_kv_plane* v_plane,
+                               const int32_t* block_table, int64_t bt_stride,
+                               const int32_t* seq_lens, int64_t num_blocks, int n_seqs,
+                               int n_q_heads, int n_kv_heads, int head_dim, int block_size,
+                               int n_splits, int max_seq_len, float* part_m, float* part_l,
+                               float* part_o, int32_t* counters, void* out, int out_dtype,
+                               int64_t out_row_stride, unsigned flags, void* stream) {
+  if (!out || !counters) return KNLP_ERR_NULL;
+  if (!dtype_ok(out_dtype)) return KNLP_ERR_DTYPE;
+  if (reinterpret_cast<uintptr_t>(part_o) % 16) return KNLP_ERR_STRIDE;  // merged as float4
+  return decode_common(query, q_dtype, q_stride, k_plane, v_plane, block_table, bt_stride,
+                       seq_lens, num_blocks, n_seqs, n_q_heads, n_kv_heads, head_dim, block_size,
+                       n_splits, max_seq_len, part_m, part_l, part_o, counters, out, out_dtype,
+                       out_row_stride, flags, stream);
 }
 
 int knlp_b200_combine(const float* part_m, const float* part_l, const float* part_o,

@@ -96,6 +96,12 @@ struct DecodeArgs {
   float* part_m;
   float* part_l;
   float* part_o;
+  // Fused finish (tensor-core kernel only; out == nullptr: partials only).  counters:
+  // one int per (sequence, head block of the launch), zero on entry and left zero.
+  void* out;
+  int out_dtype;
+  int64_t out_row_stride;
+  int* counters;
 };
 
 int launch_decode_generic(const DecodeArgs& a, cudaStream_t st);
@@ -112,6 +118,10 @@ int launch_decode_mma(const DecodeArgs& a, bool allow_tma, cudaStream_t st);
 #define KNLP_WARPS 4
 #endif
 constexpr int kDecodeWarps = KNLP_WARPS;  // 8, 4 or 2
+// The fused finish of the decode kernel merges the splits of a row group in ONE CTA:
+// worth it (it saves a launch and a pass) while the splits are few, a serial tail when
+// they are many.  Beyond this many splits the merge goes to the combine kernel.
+constexpr int kFuseMaxSplits = 64;
 constexpr int kDecodeCtasPerSm = 16 / kDecodeWarps;
 // Device-side status word of the decode kernels (0 = clean); synchronises.
 int read_and_clear_decode_status();

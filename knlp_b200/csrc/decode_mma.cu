@@ -330,6 +330,7 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   __shared__ __align__(8) uint64_t bars[kStages];  // TMA path: "stage has landed" barriers
   __shared__ unsigned slot_done[kStages];          // TMA path: warps finished with the slot
+  __shared__ int s_last;  // fused finish: this CTA completed its (sequence, head block) last
   static_assert(kStages < 8, "the page table ring has 8 slots");
   __shared__ int pg_tab[8][16];  // page ids of the stages in flight (ring, slot = stage & 7)
 
@@ -356,6 +357,76 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
   const int w_tile = warp >> hpb_log2;
   const int kvh = hb * HPB + w_head;
 
+  // Fused finish (a.out != nullptr): every CTA counts itself off on its (sequence, head
+  // block) once its partial is in global memory; the one that arrives last merges the
+  // n_splits partials of its rows into the attention output - the online-softmax
+  // recurrence across splits - which saves a second launch and a pass over the partials.
+  auto finish = [&]() {
+    if (a.out == nullptr) return;
+    __threadfence();  // this thread's partial is visible device-wide ...
+    __syncthreads();  // ... and so is every other thread's, before the CTA is counted
+    if (tid == 0) {
+      int* ctr = a.counters + (seq * gridDim.y + hb);
+      const int old = atomicAdd(ctr, 1);
+      s_last = (old == a.n_splits - 1) ? 1 : 0;
+      if (s_last) *ctr = 0;  // ready for the next launch
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // (1) one warp per row: the normalised weight of every split, w_p = l_p > 0 ?
+    // exp(m_p - max) / sum_q l_q exp(m_q - max) : 0, into shared memory (the stage
+    // buffers are free by now; the host fuses only up to kFuseMaxSplits splits)
+    const int heads = HPB * n_rep;
+    const int n = a.n_splits;
+    float* sw = reinterpret_cast<float*>(smem);  // [heads][n]
+    const int64_t row0 = static_cast<int64_t>(seq) * a.n_q_heads + hb * HPB * n_rep;
+    for (int r = warp; r < heads; r += kWarpsCta) {
+      const float* pm = a.part_m + (row0 + r) * n;
+      const float* pl = a.part_l + (row0 + r) * n;
+      float mm = -INFINITY;
+      for (int p = lane; p < n; p += 32)
+        if (__ldcg(pl + p) > 0.0f) mm = fmaxf(mm, __ldcg(pm + p));
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
+      float ll = 0.0f;
+      for (int p = lane; p < n; p += 32) {
+        const float lp = __ldcg(pl + p);
+        const float wgt = lp > 0.0f ? __expf(__ldcg(pm + p) - mm) : 0.0f;
+        sw[r * n + p] = wgt;
+        ll = fmaf(lp, wgt, ll);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ll += __shfl_xor_sync(0xffffffffu, ll, o);
+      const float inv = ll > 0.0f ? 1.0f / ll : 0.0f;  // no tokens at all: output 0
+      for (int p = lane; p < n; p += 32) sw[r * n + p] *= inv;
+    }
+    __syncthreads();
+    // (2) out[row] = sum_p w_p o_p, four elements per thread, the loads of several
+    // splits in flight at once
+    constexpr int kVec = HD / 4;
+    for (int i = tid; i < heads * kVec; i += kThreads) {
+      const int r = i / kVec, e4 = i % kVec;
+      const float4* po = reinterpret_cast<const float4*>(a.part_o + (row0 + r) * n * HD) + e4;
+      const float* wr = sw + r * n;
+      float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll 8
+      for (int p = 0; p < n; ++p) {
+        const float4 v = __ldcg(po + static_cast<int64_t>(p) * kVec);
+        const float wgt = wr[p];
+        acc.x = fmaf(v.x, wgt, acc.x);
+        acc.y = fmaf(v.y, wgt, acc.y);
+        acc.z = fmaf(v.z, wgt, acc.z);
+        acc.w = fmaf(v.w, wgt, acc.w);
+      }
+      const int64_t o = (row0 + r) * a.out_row_stride + 4 * e4;
+      store_elem_rt(a.out, o, acc.x, a.out_dtype);
+      store_elem_rt(a.out, o + 1, acc.y, a.out_dtype);
+      store_elem_rt(a.out, o + 2, acc.z, a.out_dtype);
+      store_elem_rt(a.out, o + 3, acc.w, a.out_dtype);
+    }
+  };
+
   if (end <= start) {
     // empty split: neutral partials for every q head of this head block
     const int heads = HPB * n_rep;
@@ -369,6 +440,7 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
         a.part_l[pidx] = 0.0f;
       }
     }
+    finish();
     return;
   }
 
@@ -1223,6 +1295,7 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
       a.part_l[pidx] = ll;
     }
   }
+  finish();
 }
 
 // ---------------------------------------------------------------- host side

@@ -345,12 +345,74 @@ def combine_packed(gathered: torch.Tensor, out_dtype=torch.float32) -> torch.Ten
     return out
 
 
+_counters = {}  # (device index, stream) -> zeroed int32 buffer the fused kernel leaves zero
+
+
+def _counter_buffer(dev: torch.device, n: int) -> torch.Tensor:
+    key = (dev.index, _stream(dev))
+    buf = _counters.get(key)
+    if buf is None or buf.numel() < n:
+        buf = torch.zeros(max(n, 4096), dtype=torch.int32, device=dev)
+        _counters[key] = buf
+    return buf
+
+
+def decode_attention(
+    query: torch.Tensor, k_plane: _lib.KvPlane, v_plane: _lib.KvPlane, num_blocks: int,
+    block_table: torch.Tensor, seq_lens: torch.Tensor, num_kv_heads: int, head_size: int,
+    block_size: int, *, out_dtype=None, max_seq_len: Optional[int] = None,
+    n_splits: Optional[int] = None, force_generic=False,
+) -> torch.Tensor:
+    """Split-context decode and the merge of the splits in ONE kernel launch
+    (``knlp_b200_decode_attention``).  Returns [S, Hq, d] in ``out_dtype`` (default:
+    the query's)."""
+    dev = _need_cuda(query, block_table, seq_lens)
+    if block_table.dtype != torch.int32 or seq_lens.dtype != torch.int32:
+        raise TypeError("block_table and seq_lens must be int32")
+    if block_table.dim() != 2 or block_table.stride(1) != 1 or seq_lens.dim() != 1 or (
+            seq_lens.numel() and seq_lens.stride(0) != 1):
+        raise ValueError("block_table must be [S, max_blocks] (contiguous rows), seq_lens [S]")
+    S, Hq, d = query.shape
+    if d != head_size or Hq % num_kv_heads:
+        raise ValueError("query shape does not match num_kv_heads / head_size")
+    if max_seq_len is None:
+        max_seq_len = block_table.shape[1] * block_size
+    if n_splits is None:
+        n_splits = plan_splits(S, Hq, num_kv_heads, head_size, block_size, max_seq_len)
+    ws = torch.empty((S * Hq * n_splits * (d + 2),), dtype=torch.float32, device=dev)
+    n_ml = S * Hq * n_splits
+    out = torch.empty((S, Hq, d), dtype=query.dtype if out_dtype is None else out_dtype, device=dev)
+    counters = _counter_buffer(dev, S * num_kv_heads)
+    base = ws.data_ptr()
+    with torch.cuda.device(dev):
+        rc = _lib.load().knlp_b200_decode_attention(
+            query.data_ptr(), _dt(query), _stride2(query), C.byref(k_plane), C.byref(v_plane),
+            block_table.data_ptr(), block_table.stride(0), seq_lens.data_ptr(), num_blocks,
+            S, Hq, num_kv_heads, head_size, block_size, n_splits, max_seq_len,
+            # o first: the kernel's merge reads it as float4 (16-byte aligned), m and l behind
+            base + 4 * n_ml * d, base + 4 * n_ml * (d + 1), base, counters.data_ptr(),
+            out.data_ptr(), _DT[out.dtype], d, _decode_flags(force_generic), _stream(dev))
+    _lib.check(rc, "knlp_b200_decode_attention")
+    return out
+
+
 def _decode(query, k_plane, v_plane, num_blocks, block_table, seq_lens, num_kv_heads,
-            head_size, block_size, out_dtype, max_seq_len, n_splits, force_generic):
-    pm, pl, po = decode_partials(query, k_plane, v_plane, num_blocks, block_table, seq_lens,
-                                 num_kv_heads, head_size, block_size, max_seq_len=max_seq_len,
-                                 n_splits=n_splits, force_generic=force_generic)
-    return combine_partials(pm, pl, po, out_dtype=query.dtype if out_dtype is None else out_dtype)
+            head_size, block_size, out_dtype, max_seq_len, n_splits, force_generic,
+            two_launches=True):
+    # Default: the split-context kernel, then the combine kernel.  The single-launch
+    # form (the decode kernel's last CTA per row group merges the splits) measured 1-3 %
+    # slower at every benchmark shape and is kept selectable (two_launches=False).
+    if two_launches:
+        pm, pl, po = decode_partials(query, k_plane, v_plane, num_blocks, block_table, seq_lens,
+                                     num_kv_heads, head_size, block_size,
+                                     max_seq_len=max_seq_len, n_splits=n_splits,
+                                     force_generic=force_generic)
+        return combine_partials(pm, pl, po,
+                                out_dtype=query.dtype if out_dtype is None else out_dtype)
+    return decode_attention(query, k_plane, v_plane, num_blocks, block_table, seq_lens,
+                            num_kv_heads, head_size, block_size, out_dtype=out_dtype,
+                            max_seq_len=max_seq_len, n_splits=n_splits,
+                            force_generic=force_generic)
 
 
 def fused_int4_decode(
@@ -372,6 +434,7 @@ def fused_int4_decode(
     max_seq_len: Optional[int] = None,
     n_splits: Optional[int] = None,
     force_generic: bool = False,
+    two_launches: bool = True,
 ) -> torch.Tensor:
     """Decode attention over the packed INT4 cache (reference :901-979).
 
@@ -384,7 +447,8 @@ def fused_int4_decode(
     vp = _plane(value_cache, v_scales, v_zeros if asymmetric else None,
                 _int4_mode(asymmetric, v_zeros))
     return _decode(query, kp, vp, key_cache.shape[0], block_table, seq_lens, num_kv_heads,
-                   head_size, key_cache.shape[1], out_dtype, max_seq_len, n_splits, force_generic)
+                   head_size, key_cache.shape[1], out_dtype, max_seq_len, n_splits, force_generic,
+                   two_launches)
 
 
 def kint8_vint4_decode(
@@ -405,6 +469,7 @@ def kint8_vint4_decode(
     max_seq_len: Optional[int] = None,
     n_splits: Optional[int] = None,
     force_generic: bool = False,
+    two_launches: bool = True,
 ) -> torch.Tensor:
     """K INT8 (group-32 scales) / V INT4 decode attention (reference :1496-1554)."""
     _need_cuda(key_cache_int8, value_cache_int4, k_scales, v_scales, v_zeros)
@@ -413,4 +478,4 @@ def kint8_vint4_decode(
                 _int4_mode(asymmetric, v_zeros))
     return _decode(query, kp, vp, key_cache_int8.shape[0], block_table, seq_lens, num_kv_heads,
                    head_size, key_cache_int8.shape[1], out_dtype, max_seq_len, n_splits,
-                   force_generic)
+                   force_generic, two_launches)

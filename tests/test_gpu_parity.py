@@ -275,6 +275,12 @@ def test_configs_scaled_full_compare(name, scale, cuda_device):
     assert_close(outc.cpu().numpy(), ref, name + "/TMA staging")
     # determinism: same launch twice gives identical bits
     assert torch.equal(out, w.decode(out_dtype=torch.float32))
+    # the split-context kernel followed by the combine kernel (two launches, the default)
+    # agrees with the single launch whose last CTA per row group merges the splits
+    out2 = w.decode(out_dtype=torch.float32, two_launches=False)
+    assert_close(out2.cpu().numpy(), ref, name + "/single launch")
+    assert torch.equal(out2, w.decode(out_dtype=torch.float32, two_launches=False))  # counters reset
+    assert (out2 - out).abs().max().item() < 1e-5 * max(1.0, float(np.abs(ref).max()))
 
 
 @pytest.mark.parametrize("length", [0, 1, 15, 16, 17, 31, 63, 64, 65, 127, 128, 129, 1000])
