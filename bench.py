@@ -402,7 +402,7 @@ def run_ours(args):
             "gpu_launches": (3 if ctx_mode else 2 if two_launches else 1) * K,
         }
         if world == 1 and not args.no_cpu:
-            nbytes, secs, threads, desc = cpu_reference_sample(args.workload, args.scale, 65536, 4, inner=8)
+            nbytes, secs, threads, desc = cpu_reference_sample(args.workload, args.scale, 65536, 4, inner=16)
             best = min(secs[1:])
             line["cpu_baseline"] = {"value": nbytes / best / 1e12, "unit": UNIT, "cores": threads,
                                     "kind": "port", "sample": desc + ", best of 3 after 1 warm-up",
