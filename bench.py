@@ -136,7 +136,7 @@ def cpu_reference_sample(workload: str, scale: float, sample_tokens: int, repeat
     bt = np.arange(nb, dtype=np.int32)[None]
     sl = np.array([T], np.int32)
     n_rep = hq // hkv
-    threads = min(hkv, os.cpu_count() or 1)
+    threads = min(hkv * inner, os.cpu_count() or 1)  # every (sequence, kv head) is a work unit
 
     def one_head(h):
         sl_h = slice(h, h + 1)
@@ -148,8 +148,7 @@ def cpu_reference_sample(workload: str, scale: float, sample_tokens: int, repeat
     with ThreadPoolExecutor(max_workers=threads) as ex:
         for _ in range(repeats):
             t0 = time.perf_counter()
-            for _ in range(inner):
-                list(ex.map(one_head, range(hkv)))
+            list(ex.map(one_head, [h for _ in range(inner) for h in range(hkv)]))
             secs.append(time.perf_counter() - t0)
     nbytes = inner * (T * hkv * 160 + q.size * 4 * 2 + 4 * nb)
     desc = (f"{inner} x (1 sequence x {hkv} kv heads x {T} tokens of the workload's distribution) "
@@ -161,8 +160,10 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # one step = as many sequences of the sample as keep every host core busy
+    inner = max(1, (os.cpu_count() or 8) // 8)
     nbytes, secs, threads, desc = cpu_reference_sample(args.workload, args.scale, 16384,
-                                                       args.warmup + args.steps)
+                                                       args.warmup + args.steps, inner=inner)
     secs = secs[args.warmup:]
     ms = 1e3 * sum(secs) / len(secs)
     value = nbytes / (ms / 1e3) / 1e12  # bytes of the sample / mean step time
