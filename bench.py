@@ -228,7 +228,11 @@ def run_ours(args):
     else:
         kp = _plane(w.key_cache, w.k_scales, w.k_zeros if asym else None, _int4_mode(asym, w.k_zeros))
     vasym = w.v_mode == "int4_asym"
-    vp = _plane(w.value_cache, w.v_scales, w.v_zeros if vasym else None, _int4_mode(vasym, w.v_zeros))
+    if w.v_mode == "int8":
+        vp = _plane(w.value_cache, w.v_scales, None, _lib.KV_INT8_G32)
+    else:
+        vp = _plane(w.value_cache, w.v_scales, w.v_zeros if vasym else None,
+                    _int4_mode(vasym, w.v_zeros))
     nblocks = w.key_cache.shape[0]
 
     two_launches = (not args.single_launch) or ctx_mode

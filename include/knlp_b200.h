@@ -20,6 +20,8 @@
  *   reshape_and_cache_k_int8        :1287-1312 -> knlp_b200_quant_append (K mode INT8_G32)
  *   fused_int4_decode               :901-979   -> knlp_b200_decode_splitk + knlp_b200_combine
  *   kint8_vint4_decode              :1496-1554 -> same, K mode INT8_G32
+ *   reshape_and_cache_v_int8        :1619-1645 -> knlp_b200_quant_append (V mode INT8_G32)
+ *   kint8_vint8_decode              :1796-1843 -> decode entry points, both modes INT8_G32
  * Cache layouts are the reference's (:213-223): codes [num_blocks, block_size,
  * num_kv_heads, head_size/2] uint8 (INT4; element 2j in the low nibble of byte j)
  * or [.., head_size] int8 (INT8); scales and zeros [.., head_size/32] fp16.

@@ -13,7 +13,7 @@ bool dtype_ok(int dt) { return dt == KNLP_F32 || dt == KNLP_F16 || dt == KNLP_BF
 
 bool head_dim_ok(int d) { return d == 32 || d == 64 || d == 128 || d == 256; }
 
-int check_plane(const knlp_kv_plane* p, bool is_k) {
+int check_plane(const knlp_kv_plane* p, bool /*is_k*/) {
   if (!p) return KNLP_ERR_NULL;
   switch (p->mode) {
     case KNLP_KV_INT4_SYM:
@@ -22,7 +22,6 @@ int check_plane(const knlp_kv_plane* p, bool is_k) {
       if (!p->zeros) return KNLP_ERR_NULL;
       break;
     case KNLP_KV_INT8_G32:
-      if (!is_k) return KNLP_ERR_MODE;  // int8 V is not built
       break;
     default:
       return KNLP_ERR_MODE;

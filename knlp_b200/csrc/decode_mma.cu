@@ -76,7 +76,7 @@ constexpr int kThreads = kWarpsCta * 32;
 #ifndef KNLP_STAGES
 #define KNLP_STAGES 4
 #endif
-constexpr int kStages = KNLP_STAGES;
+constexpr int kMaxStages = KNLP_STAGES;  // pipeline depth; one less where shared memory is short
 constexpr int kRows = kWarpsCta * 16;  // (token, head) rows per stage
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -261,15 +261,25 @@ __device__ __forceinline__ void unpack_int8x4(uint32_t w, uint32_t out[2]) {
   out[1] = __byte_perm(u, 0u, 0x4342);
 }
 
+// A transposed int8 V register: bytes 0, 1 = elements d, d+1 of one token, bytes 2, 3 the
+// same elements of the next token.  Biased to unsigned and split by element:
+// out[0] = (d of both tokens), out[1] = (d+1 of both tokens), fp16 subnormals * 2^-24.
+__device__ __forceinline__ void unpack_int8_pairs(uint32_t w, uint32_t out[2]) {
+  const uint32_t u = w ^ 0x80808080u;
+  out[0] = u & 0x00FF00FFu;
+  out[1] = __byte_perm(u, 0u, 0x4341);
+}
+
 // Shared-memory geometry of a stage.  PAD = 16 (cp.async path) separates the 16-row
 // code tiles of the eight warps by one extra 16-byte piece, so that a warp-wide copy
 // of one token row (all heads, 512 contiguous bytes) lands in distinct banks.
-template <int HD, int KMODE, int PAD>
+template <int HD, int KMODE, int VMODE, int PAD>
 struct Geo {
   static constexpr bool kInt8K = (KMODE == KNLP_KV_INT8_G32);
+  static constexpr bool kInt8V = (VMODE == KNLP_KV_INT8_G32);
   static constexpr int NG = HD / 32;
   static constexpr int KB = kInt8K ? HD : HD / 2;  // K row bytes
-  static constexpr int VB = HD / 2;                // V row bytes
+  static constexpr int VB = kInt8V ? HD : HD / 2;  // V row bytes
   static constexpr int KCH = KB / 16;              // 16-byte pieces per K row
   static constexpr int VCH = VB / 16;
   static constexpr int SB = NG * 2;                // scale row bytes
@@ -282,6 +292,10 @@ struct Geo {
   static constexpr int kOffVs = kOffKz + kRows * SB;
   static constexpr int kOffVz = kOffVs + kRows * SB;
   static constexpr int kStageBytes = kOffVz + kRows * SB;
+  // Four stages, or three where four would no longer let kCtasPerSm CTAs share the
+  // 227 KB of an SM (the INT8 planes); depth 3 and 4 measured the same.
+  static constexpr int kStages =
+      kCtasPerSm * (kMaxStages * kStageBytes + 2048) <= 232448 ? kMaxStages : kMaxStages - 1;
   static constexpr int kSmemBytes = kStages * kStageBytes;
 };
 
@@ -319,7 +333,9 @@ __device__ __forceinline__ bool run_stages(F& f, int it0, int n) {
 template <int HD, int KMODE, int VMODE, bool SPLIT, bool TMA, int HPBL>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant__ TmaMaps tm) {
-  using G = Geo<HD, KMODE, TMA ? 0 : 16>;
+  using G = Geo<HD, KMODE, VMODE, TMA ? 0 : 16>;
+  constexpr int kStages = G::kStages;
+  constexpr bool kInt8V = G::kInt8V;
   constexpr int NG = G::NG;
   constexpr bool kInt8K = G::kInt8K;
   constexpr bool kAsymK = (KMODE == KNLP_KV_INT4_ASYM);
@@ -328,10 +344,10 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
   extern __shared__ uint8_t smem_raw[];
   // swizzled TMA tiles need their natural alignment: round the base up to 1 KB
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  __shared__ __align__(8) uint64_t bars[kStages];  // TMA path: "stage has landed" barriers
-  __shared__ unsigned slot_done[kStages];          // TMA path: warps finished with the slot
+  __shared__ __align__(8) uint64_t bars[kMaxStages];  // TMA path: "stage has landed" barriers
+  __shared__ unsigned slot_done[kMaxStages];          // TMA path: warps finished with the slot
   __shared__ int s_last;  // fused finish: this CTA completed its (sequence, head block) last
-  static_assert(kStages < 8, "the page table ring has 8 slots");
+  static_assert(kMaxStages < 8, "the page table ring has 8 slots");
   __shared__ int pg_tab[8][16];  // page ids of the stages in flight (ring, slot = stage & 7)
 
   const int tid = threadIdx.x;
@@ -535,7 +551,7 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
   const uint32_t smem_base = smem_u32(smem);
   constexpr int kKPer = G::KCH / 2, kVPer = G::VCH / 2;  // pieces per thread and stage
   constexpr int kKChLog = G::KCH == 8 ? 3 : G::KCH == 4 ? 2 : 1;
-  constexpr int kVChLog = G::VCH == 4 ? 2 : 1;
+  constexpr int kVChLog = G::VCH == 8 ? 3 : G::VCH == 4 ? 2 : 1;
   const int k_lg = hpb_log2 + kKChLog, v_lg = hpb_log2 + kVChLog;
   const int k_tt0 = tid >> k_lg, v_tt0 = tid >> v_lg;       // token of piece 0 in the stage
   const int k_dtt = kThreads >> k_lg, v_dtt = kThreads >> v_lg;  // token step between pieces
@@ -891,7 +907,8 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
   const uint32_t v_lm0 = smem_base + G::kOffV + warp * G::kTileV + lm_row * G::VB;
   // piece offsets of the ldmatrix calls (piece index xor row swizzle), fixed per thread
   constexpr int kKLoads = kInt8K ? NG : NG / 2;
-  uint32_t k_lm[kKLoads], v_lm[NG / 2];
+  constexpr int kVLoads = kInt8V ? NG : NG / 2;
+  uint32_t k_lm[kKLoads], v_lm[kVLoads];
 #pragma unroll
   for (int i = 0; i < kKLoads; ++i) {
     if constexpr (TMA) {
@@ -902,7 +919,7 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
     }
   }
 #pragma unroll
-  for (int i = 0; i < NG / 2; ++i) {
+  for (int i = 0; i < kVLoads; ++i) {
     if constexpr (TMA) {
       v_lm[i] = smem_base + G::kOffV +
                 code_off(G::VB, v_seg, v_box, w_tile, w_head, lm_row, 2 * i + lm_q);
@@ -1130,7 +1147,7 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
         }
       } else {
 #pragma unroll
-        for (int g = 0; g < NG; ++g) vz[g] = -8.0f * vs[rh][g];
+        for (int g = 0; g < NG; ++g) vz[g] = (kInt8V ? -128.0f : -8.0f) * vs[rh][g];
       }
       if (partial && (tok0 + fr + rh * 8) >= end) {
 #pragma unroll
@@ -1145,35 +1162,59 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
         for (int g = 0; g < NG; ++g) zacc[g][h] = fmaf(pr[rh][h], vz[g], zacc[g][h]);
     }
 
+    // P' of group g as the B operand: rows = the 16 tokens (two registers), columns as
+    // in the score accumulators
+    auto p_operand = [&](int g, uint32_t pb[2]) {
 #pragma unroll
-    for (int gp = 0; gp < NG / 2; ++gp) {
-      uint32_t w[4];
-      ldmatrix_x4_trans_at<stage_off>(v_lm[gp], w);
-      // w0: tokens 0-7 group 2gp; w1: tokens 8-15 group 2gp; w2/w3: group 2gp+1
-#pragma unroll
-      for (int s = 0; s < 2; ++s) {
-        const int g = 2 * gp + s;
-        uint32_t pb[2];
-#pragma unroll
-        for (int rh = 0; rh < 2; ++rh) {
-          uint32_t packed;
-          if constexpr (SPLIT) {
-            // hi = x with the low 13 mantissa bits cleared (exact in fp16), lo = x - hi
-            const float x = pr[rh][0] * vs[rh][g];
-            const float hi = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
-            packed = pack_f2h2(hi, x - hi);
-          } else {
-            packed = pack_f2h2(pr[rh][0] * vs[rh][g], pr[rh][1] * vs[rh][g]);
-          }
-          pb[rh] = movmatrix_trans(packed);
+      for (int rh = 0; rh < 2; ++rh) {
+        uint32_t packed;
+        if constexpr (SPLIT) {
+          // hi = x with the low 13 mantissa bits cleared (exact in fp16), lo = x - hi
+          const float x = pr[rh][0] * vs[rh][g];
+          const float hi = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
+          packed = pack_f2h2(hi, x - hi);
+        } else {
+          packed = pack_f2h2(pr[rh][0] * vs[rh][g], pr[rh][1] * vs[rh][g]);
         }
-        // a ldmatrix.trans register is (token 2ft | token 2ft+1) x nibbles 4fr..4fr+3 of
-        // the group, so the same unpack yields (token, token+1) pairs per element
-        uint32_t e0[4], e1[4];
-        unpack_nibbles8(w[2 * s], e0);
-        unpack_nibbles8(w[2 * s + 1], e1);
-        mma16816(oacc[g][0], e0[0], e0[1], e1[0], e1[1], pb[0], pb[1]);
-        mma16816(oacc[g][1], e0[2], e0[3], e1[2], e1[3], pb[0], pb[1]);
+        pb[rh] = movmatrix_trans(packed);
+      }
+    };
+    if constexpr (kInt8V) {
+#pragma unroll
+      for (int g = 0; g < NG; ++g) {
+        uint32_t w[4];
+        ldmatrix_x4_trans_at<stage_off>(v_lm[g], w);
+        // w0: tokens 0-7, 16-byte piece 2g; w1: tokens 8-15, piece 2g; w2 / w3: piece 2g+1.
+        // A register holds elements 2fr, 2fr+1 of its piece for tokens 2ft and 2ft+1.
+        uint32_t pb[2];
+        p_operand(g, pb);
+        uint32_t a0[2], a1[2], b0[2], b1[2];
+        unpack_int8_pairs(w[0], a0);
+        unpack_int8_pairs(w[1], a1);
+        unpack_int8_pairs(w[2], b0);
+        unpack_int8_pairs(w[3], b1);
+        mma16816(oacc[g][0], a0[0], a0[1], a1[0], a1[1], pb[0], pb[1]);
+        mma16816(oacc[g][1], b0[0], b0[1], b1[0], b1[1], pb[0], pb[1]);
+      }
+    } else {
+#pragma unroll
+      for (int gp = 0; gp < NG / 2; ++gp) {
+        uint32_t w[4];
+        ldmatrix_x4_trans_at<stage_off>(v_lm[gp], w);
+        // w0: tokens 0-7 group 2gp; w1: tokens 8-15 group 2gp; w2/w3: group 2gp+1
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          const int g = 2 * gp + s;
+          uint32_t pb[2];
+          p_operand(g, pb);
+          // a ldmatrix.trans register is (token 2ft | token 2ft+1) x nibbles 4fr..4fr+3 of
+          // the group, so the same unpack yields (token, token+1) pairs per element
+          uint32_t e0[4], e1[4];
+          unpack_nibbles8(w[2 * s], e0);
+          unpack_nibbles8(w[2 * s + 1], e1);
+          mma16816(oacc[g][0], e0[0], e0[1], e1[0], e1[1], pb[0], pb[1]);
+          mma16816(oacc[g][1], e0[2], e0[3], e1[2], e1[3], pb[0], pb[1]);
+        }
       }
     }
     if constexpr (TMA) release_slot(it, stage_tag);  // done reading the stage
@@ -1228,6 +1269,29 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
     float* wo = sm_o + warp * kHeadSlots * HD;
 #pragma unroll
     for (int g = 0; g < NG; ++g) {
+      if constexpr (kInt8V) {
+        // accumulator j of the group = its 16-byte piece j; rows fr | fr + 8 = elements
+        // 2fr | 2fr + 1 of the piece, all scaled 2^-24
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int dj = 32 * g + 16 * j + 2 * fr;
+          if constexpr (SPLIT) {
+            float2 v;
+            v.x = fmaf(oacc[g][j][0] + oacc[g][j][1], kTwo24, zacc[g][0]);
+            v.y = fmaf(oacc[g][j][2] + oacc[g][j][3], kTwo24, zacc[g][0]);
+            *reinterpret_cast<float2*>(wo + ft * HD + dj) = v;
+          } else {
+            float2 v0, v1;
+            v0.x = fmaf(oacc[g][j][0], kTwo24, zacc[g][0]);
+            v0.y = fmaf(oacc[g][j][2], kTwo24, zacc[g][0]);
+            v1.x = fmaf(oacc[g][j][1], kTwo24, zacc[g][NH - 1]);
+            v1.y = fmaf(oacc[g][j][3], kTwo24, zacc[g][NH - 1]);
+            *reinterpret_cast<float2*>(wo + (2 * ft) * HD + dj) = v0;
+            *reinterpret_cast<float2*>(wo + (2 * ft + 1) * HD + dj) = v1;
+          }
+        }
+        continue;
+      }
       const int d0 = 32 * g + 4 * fr;
       // undo the 2^-24 of the subnormals; odd rows = (mixed - even) / 16
       if constexpr (SPLIT) {
@@ -1415,6 +1479,7 @@ struct MapKey {
 
 bool build_maps(const DecodeArgs& a, int hpb, TmaMaps* out) {
   if (a.block_size < 16) return false;
+  if (a.v.mode == KNLP_KV_INT8_G32) return false;  // INT8 V is staged with cp.async only
   const int ng = a.head_dim / 32, sb = ng * 2;
   // every TMA destination (a scale box is 16 tokens x hpb heads) must be 128-byte aligned
   if ((16 * sb * hpb) % 128) return false;
@@ -1456,7 +1521,7 @@ bool build_maps(const DecodeArgs& a, int hpb, TmaMaps* out) {
   m.scale_merged = merged ? 1 : 0;
   const int kb = a.k.mode == KNLP_KV_INT8_G32 ? a.head_dim : a.head_dim / 2;
   const int kform = codes_map(&m.k, a.k, kb, hpb, a);
-  const int vform = codes_map(&m.v, a.v, a.head_dim / 2, hpb, a);
+  const int vform = codes_map(&m.v, a.v, a.head_dim / 2, hpb, a);  // (INT8 V never gets here)
   if (kform == 0 || vform == 0) return false;
   m.k_narrow = kform == 2;
   m.v_narrow = vform == 2;
@@ -1474,7 +1539,7 @@ bool build_maps(const DecodeArgs& a, int hpb, TmaMaps* out) {
 
 template <int HD, int KMODE, int VMODE, bool SPLIT, bool TMA, int HPBL>
 int launch_hpb(const DecodeArgs& a, const MmaParams& mp, const TmaMaps& tm, cudaStream_t st) {
-  using G = Geo<HD, KMODE, TMA ? 0 : 16>;
+  using G = Geo<HD, KMODE, VMODE, TMA ? 0 : 16>;
   constexpr int kSmem = G::kSmemBytes + 1024;  // slack for the 1 KB alignment of the stages
   auto kern = decode_mma_kernel<HD, KMODE, VMODE, SPLIT, TMA, HPBL>;
   static int configured_dev = -1;  // per instantiation; the attribute is per device function
@@ -1530,6 +1595,8 @@ int launch_modes(const DecodeArgs& a, const MmaParams& mp, bool split, const Tma
     return launch_split<HD, KNLP_KV_INT8_G32, KNLP_KV_INT4_ASYM>(a, mp, split, tm, st);
   if (km == KNLP_KV_INT8_G32 && vm == KNLP_KV_INT4_SYM)
     return launch_split<HD, KNLP_KV_INT8_G32, KNLP_KV_INT4_SYM>(a, mp, split, tm, st);
+  if (km == KNLP_KV_INT8_G32 && vm == KNLP_KV_INT8_G32)
+    return launch_split<HD, KNLP_KV_INT8_G32, KNLP_KV_INT8_G32>(a, mp, split, tm, st);
   return 1;  // other combinations go to the generic kernel
 }
 
@@ -1575,7 +1642,8 @@ int launch_decode_mma(const DecodeArgs& a, bool allow_tma, cudaStream_t st) {
   const int hpb = 1 << mp.hpb_log2;
   const int kb = a.k.mode == KNLP_KV_INT8_G32 ? a.head_dim : a.head_dim / 2;
   if (!plane_ok(a.k, a.head_dim, kb, hpb, a.n_kv_heads) ||
-      !plane_ok(a.v, a.head_dim, a.head_dim / 2, hpb, a.n_kv_heads))
+      !plane_ok(a.v, a.head_dim, a.v.mode == KNLP_KV_INT8_G32 ? a.head_dim : a.head_dim / 2, hpb,
+                a.n_kv_heads))
     return 1;
   mp.page_log2 = 0;
   while ((1 << mp.page_log2) < a.block_size) ++mp.page_log2;

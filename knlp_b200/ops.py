@@ -188,6 +188,19 @@ def reshape_and_cache_k_int8(
     _quant_append(key, None, kp, None, slot_mapping, key.shape[2], key_cache_int8.shape[1], 0.0)
 
 
+def reshape_and_cache_v_int8(
+    value: torch.Tensor,
+    value_cache_int8: torch.Tensor,  # [num_blocks, block_size, num_heads, head_size] int8
+    v_scales: torch.Tensor,
+    slot_mapping: torch.Tensor,
+) -> None:
+    """V -> symmetric INT8 with per-group-32 fp16 scales (reference :1619-1645)."""
+    _need_cuda(value_cache_int8, v_scales)
+    vp = _plane(value_cache_int8, v_scales, None, _lib.KV_INT8_G32)
+    _quant_append(None, value, None, vp, slot_mapping, value.shape[2],
+                  value_cache_int8.shape[1], 0.0)
+
+
 def plan_splits(num_seqs: int, num_heads: int, num_kv_heads: int, head_size: int,
                 block_size: int, max_seq_len: int) -> int:
     """Split count the library recommends for this decode shape (host arithmetic)."""
@@ -476,6 +489,33 @@ def kint8_vint4_decode(
     kp = _plane(key_cache_int8, k_scales, None, _lib.KV_INT8_G32)
     vp = _plane(value_cache_int4, v_scales, v_zeros if asymmetric else None,
                 _int4_mode(asymmetric, v_zeros))
+    return _decode(query, kp, vp, key_cache_int8.shape[0], block_table, seq_lens, num_kv_heads,
+                   head_size, key_cache_int8.shape[1], out_dtype, max_seq_len, n_splits,
+                   force_generic, two_launches)
+
+
+def kint8_vint8_decode(
+    query: torch.Tensor,
+    key_cache_int8: torch.Tensor,  # [num_blocks, block_size, kv_heads, head_size] int8
+    value_cache_int8: torch.Tensor,  # same shape, int8
+    k_scales: torch.Tensor,
+    v_scales: torch.Tensor,
+    block_table: torch.Tensor,
+    seq_lens: torch.Tensor,
+    num_kv_heads: int,
+    head_size: int,
+    block_n: int = 64,
+    *,
+    out_dtype: Optional[torch.dtype] = None,
+    max_seq_len: Optional[int] = None,
+    n_splits: Optional[int] = None,
+    force_generic: bool = False,
+    two_launches: bool = True,
+) -> torch.Tensor:
+    """K INT8 / V INT8 decode attention, group-32 scales on both (reference :1796-1843)."""
+    _need_cuda(key_cache_int8, value_cache_int8, k_scales, v_scales)
+    kp = _plane(key_cache_int8, k_scales, None, _lib.KV_INT8_G32)
+    vp = _plane(value_cache_int8, v_scales, None, _lib.KV_INT8_G32)
     return _decode(query, kp, vp, key_cache_int8.shape[0], block_table, seq_lens, num_kv_heads,
                    head_size, key_cache_int8.shape[1], out_dtype, max_seq_len, n_splits,
                    force_generic, two_launches)

@@ -48,7 +48,7 @@ class Workload:
     def kv_bytes_per_token_head(self) -> int:
         d, ng = self.head_dim, self.head_dim // 32
         kb = d + 2 * ng if self.k_mode == "int8" else d // 2 + (4 * ng if self.k_mode == "int4_asym" else 2 * ng)
-        vb = d // 2 + (4 * ng if self.v_mode == "int4_asym" else 2 * ng)
+        vb = d + 2 * ng if self.v_mode == "int8" else d // 2 + (4 * ng if self.v_mode == "int4_asym" else 2 * ng)
         return kb + vb
 
     def algorithmic_bytes(self) -> int:
@@ -61,6 +61,11 @@ class Workload:
         return toks * self.n_kv_heads * self.kv_bytes_per_token_head() + qo + 4 * pages
 
     def decode(self, **kw) -> torch.Tensor:
+        if self.k_mode == "int8" and self.v_mode == "int8":
+            return ops.kint8_vint8_decode(
+                self.query, self.key_cache, self.value_cache, self.k_scales, self.v_scales,
+                self.block_table, self.seq_lens, self.n_kv_heads, self.head_dim,
+                max_seq_len=self.max_seq_len, **kw)
         if self.k_mode == "int8":
             return ops.kint8_vint4_decode(
                 self.query, self.key_cache, self.value_cache, self.k_scales, self.v_scales,
@@ -92,7 +97,8 @@ def alloc_cache(num_blocks: int, n_kv_heads: int, head_dim: int, k_mode: str, v_
     kw = head_dim if k_mode == "int8" else head_dim // 2
     kc = torch.zeros(num_blocks, page, n_kv_heads, kw, device=device,
                      dtype=torch.int8 if k_mode == "int8" else torch.uint8)
-    vc = torch.zeros(num_blocks, page, n_kv_heads, head_dim // 2, device=device, dtype=torch.uint8)
+    vc = torch.zeros(num_blocks, page, n_kv_heads, head_dim if v_mode == "int8" else head_dim // 2,
+                     device=device, dtype=torch.int8 if v_mode == "int8" else torch.uint8)
     mk = lambda: torch.zeros(num_blocks, page, n_kv_heads, ng, device=device, dtype=torch.float16)
     ks, vs = mk(), mk()
     kz = mk() if k_mode == "int4_asym" else None
@@ -104,7 +110,11 @@ def append_tokens(w_or_caches, key, value, slots, k_mode, v_mode):
     kc, vc, ks, vs, kz, vz = w_or_caches
     if k_mode == "int8":
         ops.reshape_and_cache_k_int8(key, kc, ks, slots)
-        ops.reshape_and_cache_v_only_int4(value, vc, vs, slots, vz, asymmetric=v_mode == "int4_asym")
+        if v_mode == "int8":
+            ops.reshape_and_cache_v_int8(value, vc, vs, slots)
+        else:
+            ops.reshape_and_cache_v_only_int4(value, vc, vs, slots, vz,
+                                              asymmetric=v_mode == "int4_asym")
     else:
         ops.reshape_and_cache_int4(key, value, kc, vc, ks, vs, slots, kz, vz,
                                    asymmetric=k_mode == "int4_asym")
@@ -233,6 +243,15 @@ def config(name: str, device, *, seed: Optional[int] = None, scale: float = 1.0,
         return build(name, n_seqs=128, n_q_heads=32, n_kv_heads=8, head_dim=128,
                      seq_lens=[ctx(L) for L in lens], seed=5000 if seed is None else seed,
                      device=device, k_mode="int8", v_mode="int4_asym", shuffle_pages=True,
+                     head_slice=head_slice, extra_blocks_per_seq=max(4, extra_blocks_per_seq),
+                     ctx_shard=ctx_shard)
+    if name == "k8v8":
+        # the mixed workload's batch with both planes INT8 (kint8_vint8_decode)
+        g = torch.Generator().manual_seed(5000 if seed is None else seed)
+        lens = torch.randint(512, 4097, (128,), generator=g).tolist()
+        return build(name, n_seqs=128, n_q_heads=32, n_kv_heads=8, head_dim=128,
+                     seq_lens=[ctx(L) for L in lens], seed=5000 if seed is None else seed,
+                     device=device, k_mode="int8", v_mode="int8", shuffle_pages=True,
                      head_slice=head_slice, extra_blocks_per_seq=max(4, extra_blocks_per_seq),
                      ctx_shard=ctx_shard)
     raise ValueError(f"unknown workload {name}")

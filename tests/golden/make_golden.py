@@ -195,15 +195,60 @@ def gen_plugin_cases(out):
     print("plugin quantizers done", flush=True)
 
 
+def gen_v8_cases(m, out):
+    """INT8 V: reshape_and_cache_v_int8 (:1619-1645) and kint8_vint8_decode (:1796-1843) on
+    the inputs of the write and decode cases above (read back from their files)."""
+    rec = {}
+    for name in ("write_f32_d64", "write_bf16_d128", "write_f16_d128"):
+        G = np.load(os.path.join(HERE, name + ".npz"))
+        dt = DT[str(G["src_dtype"])]
+        v = torch.from_numpy(G["value"]).to(dt)
+        slots = torch.from_numpy(G["slot_mapping"])
+        n, h, d = v.shape
+        nb, P = int(G["num_blocks"]), int(G["block_size"])
+        vc8 = torch.zeros(nb, P, h, d, dtype=torch.int8)
+        vs = torch.zeros(nb, P, h, d // 32, dtype=torch.float16)
+        m.reshape_and_cache_v_int8(v, vc8, vs, slots)
+        rec[name + "_vc8"] = vc8.numpy().copy()
+        rec[name + "_vs8"] = f16_bits(vs)
+        print("v8 write", name, "done", flush=True)
+    for name in ("decode_mha_f32_d64", "decode_gqa4_bf16_d128", "decode_gqa8_f16_d128"):
+        G = np.load(os.path.join(HERE, name + ".npz"))
+        dt = DT[str(G["q_dtype"])]
+        q = torch.from_numpy(G["query"]).to(dt)
+        k = torch.from_numpy(G["key"]).to(dt)
+        v = torch.from_numpy(G["value"]).to(dt)
+        slots = torch.from_numpy(G["slot_mapping"])
+        bt = torch.from_numpy(G["block_table"])
+        seq_lens = torch.from_numpy(G["seq_lens"])
+        nb, P = int(G["num_blocks"]), int(G["block_size"])
+        hkv, d = int(G["num_kv_heads"]), int(G["head_size"])
+        kc8 = torch.zeros(nb, P, hkv, d, dtype=torch.int8)
+        vc8 = torch.zeros(nb, P, hkv, d, dtype=torch.int8)
+        ks = torch.zeros(nb, P, hkv, d // 32, dtype=torch.float16)
+        vs = torch.zeros(nb, P, hkv, d // 32, dtype=torch.float16)
+        m.reshape_and_cache_k_int8(k, kc8, ks, slots)
+        m.reshape_and_cache_v_int8(v, vc8, vs, slots)
+        o = m.kint8_vint8_decode(q, kc8, vc8, ks, vs, bt, seq_lens, hkv, d, block_n=64)
+        rec[name + "_k8v8_out"] = o.float().numpy()
+        print("v8 decode", name, "done", flush=True)
+    out["v8_modes"] = rec
+
+
 def main():
     out = {}
     if "--only-plugin" in sys.argv:
         gen_plugin_cases(out)
+    elif "--only-v8" in sys.argv:
+        gen_v8_cases(load_reference(), out)
     else:
         m = load_reference()
         gen_write_cases(m, out)
         gen_decode_cases(m, out)
         gen_plugin_cases(out)
+        for name, rec in out.items():  # gen_v8_cases reads the files written so far
+            np.savez_compressed(os.path.join(HERE, name + ".npz"), **rec)
+        gen_v8_cases(m, out)
     for name, rec in out.items():
         np.savez_compressed(os.path.join(HERE, name + ".npz"), **rec)
         print("saved", name)

@@ -66,7 +66,7 @@ def test_argument_errors_are_reported_on_the_host(lib):
     rc = lib.knlp_b200_decode_splitk(p, 0, st2, null, null, p, 1, p, 1, 1, 4, 4, 64, 16, 1, 16,
                                      p, p, p, 0, null)
     assert rc == -1
-    # asymmetric plane without zeros; int8 V
+    # asymmetric plane without zeros; unknown mode
     pl = _lib.KvPlane()
     pl.codes = p.value
     pl.scales = p.value
@@ -75,7 +75,7 @@ def test_argument_errors_are_reported_on_the_host(lib):
                                      16, 1, 16, p, p, p, 0, null)
     assert rc == -1
     pk = _lib.KvPlane(); pk.codes = p.value; pk.scales = p.value; pk.mode = _lib.KV_INT4_SYM
-    pv = _lib.KvPlane(); pv.codes = p.value; pv.scales = p.value; pv.mode = _lib.KV_INT8_G32
+    pv = _lib.KvPlane(); pv.codes = p.value; pv.scales = p.value; pv.mode = 7  # no such mode
     rc = lib.knlp_b200_decode_splitk(p, 0, st2, C.byref(pk), C.byref(pv), p, 1, p, 1, 1, 4, 4, 64,
                                      16, 1, 16, p, p, p, 0, null)
     assert rc == -4
