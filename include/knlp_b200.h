@@ -22,6 +22,8 @@
  *   kint8_vint4_decode              :1496-1554 -> same, K mode INT8_G32
  *   reshape_and_cache_v_int8        :1619-1645 -> knlp_b200_quant_append (V mode INT8_G32)
  *   kint8_vint8_decode              :1796-1843 -> decode entry points, both modes INT8_G32
+ *   kfp16_vint4_decode              :1159-1224 -> decode entry points, K mode F16 / BF16
+ *   kfp16_vint8_decode              :1975-2028 -> same, V mode INT8_G32
  * Cache layouts are the reference's (:213-223): codes [num_blocks, block_size,
  * num_kv_heads, head_size/2] uint8 (INT4; element 2j in the low nibble of byte j)
  * or [.., head_size] int8 (INT8); scales and zeros [.., head_size/32] fp16.
@@ -57,7 +59,13 @@ typedef enum {
   KNLP_KV_NONE = 0,      /* plane absent (skip) */
   KNLP_KV_INT4_SYM = 1,  /* offset-binary nibbles, scale only (reference :328-357) */
   KNLP_KV_INT4_ASYM = 2, /* unsigned nibbles, scale + zero (reference :308-327) */
-  KNLP_KV_INT8_G32 = 3   /* int8 codes, per-group-32 scale (reference :1270-1284) */
+  KNLP_KV_INT8_G32 = 3,  /* int8 codes, per-group-32 scale (reference :1270-1284) */
+  /* Unquantized K plane of the hybrid decodes (reference kfp16_vint4_decode :1159-1224,
+   * kfp16_vint8_decode :1975-2028): codes points to [.., head_size] fp16 or bf16 values,
+   * codes_stride counts those 2-byte elements, scales / zeros are unused (may be NULL).
+   * Decode only, K side only; runs on the stride-generic kernel. */
+  KNLP_KV_F16 = 4,
+  KNLP_KV_BF16 = 5
 } knlp_kv_mode;
 
 /* One cache plane (K or V).  Strides are in ELEMENTS of the array they index

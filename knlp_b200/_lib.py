@@ -18,6 +18,7 @@ ABI_VERSION = 1
 # dtype / mode codes of include/knlp_b200.h
 F32, F16, BF16 = 0, 1, 2
 KV_NONE, KV_INT4_SYM, KV_INT4_ASYM, KV_INT8_G32 = 0, 1, 2, 3
+KV_F16, KV_BF16 = 4, 5  # unquantized K plane of the kfp16_* decodes
 DECODE_FORCE_GENERIC = 1
 DECODE_USE_TMA = 2
 

@@ -13,9 +13,14 @@ bool dtype_ok(int dt) { return dt == KNLP_F32 || dt == KNLP_F16 || dt == KNLP_BF
 
 bool head_dim_ok(int d) { return d == 32 || d == 64 || d == 128 || d == 256; }
 
-int check_plane(const knlp_kv_plane* p, bool /*is_k*/) {
+// unquantized_k: the plane may also be an fp16 / bf16 K plane (decode only).
+int check_plane(const knlp_kv_plane* p, bool unquantized_k) {
   if (!p) return KNLP_ERR_NULL;
   switch (p->mode) {
+    case KNLP_KV_F16:
+    case KNLP_KV_BF16:
+      if (!unquantized_k) return KNLP_ERR_MODE;
+      return p->codes ? KNLP_OK : KNLP_ERR_NULL;
     case KNLP_KV_INT4_SYM:
       break;
     case KNLP_KV_INT4_ASYM:
@@ -82,7 +87,7 @@ int knlp_b200_quant_append(const void* key, const int64_t key_stride[2], const v
   const bool do_v = value && v_plane && v_plane->mode != KNLP_KV_NONE;
   if (do_k) {
     if (!key_stride) return KNLP_ERR_NULL;
-    int rc = check_plane(k_plane, true);
+    int rc = check_plane(k_plane, false);
     if (rc) return rc;
   }
   if (do_v) {

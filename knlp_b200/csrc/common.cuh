@@ -38,6 +38,10 @@ inline Plane make_plane(const knlp_kv_plane* p) {
     d.zs[i] = p->zeros ? p->zeros_stride[i] : 0;
   }
   d.mode = p->mode;
+  if (p->mode == KNLP_KV_F16 || p->mode == KNLP_KV_BF16) {
+    // an unquantized plane: its strides arrive in 2-byte elements, the kernels index bytes
+    for (int i = 0; i < 3; ++i) d.cs[i] *= 2;
+  }
   return d;
 }
 

@@ -27,6 +27,14 @@ __device__ __forceinline__ void load_row(const Plane& p, const uint8_t* crow, co
   for (int i = 0; i < EPL; ++i) {
     const int e = lane * EPL + i;
     const int g = e >> 5;
+    if (p.mode == KNLP_KV_F16) {  // unquantized K (kfp16_* decodes, reference :1076-1083)
+      out[i] = __half2float(reinterpret_cast<const __half*>(crow)[e]);
+      continue;
+    }
+    if (p.mode == KNLP_KV_BF16) {
+      out[i] = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(crow)[e]);
+      continue;
+    }
     const float s = __half2float(srow[g]);
     if (p.mode == KNLP_KV_INT8_G32) {
       out[i] = static_cast<float>(static_cast<int8_t>(crow[e])) * s;

@@ -8,6 +8,10 @@ Drop-in for the module-level functions of mcgrof/knlp's
     reshape_and_cache_k_int8        (:1287-1312)
     fused_int4_decode               (:901-979)
     kint8_vint4_decode              (:1496-1554)
+    reshape_and_cache_v_int8        (:1619-1645)
+    kint8_vint8_decode              (:1796-1843)
+    kfp16_vint4_decode              (:1159-1224)   stride-generic kernel
+    kfp16_vint8_decode              (:1975-2028)   stride-generic kernel
 
 Same argument names, order, meaning and in-place behaviour; tensors are CUDA
 tensors owned by the caller.  The work is done by hand-written sm_100a kernels in
@@ -519,3 +523,70 @@ def kint8_vint8_decode(
     return _decode(query, kp, vp, key_cache_int8.shape[0], block_table, seq_lens, num_kv_heads,
                    head_size, key_cache_int8.shape[1], out_dtype, max_seq_len, n_splits,
                    force_generic, two_launches)
+
+
+def _fp_plane(cache: torch.Tensor) -> _lib.KvPlane:
+    """An unquantized [num_blocks, block_size, kv_heads, head_size] fp16 / bf16 K cache."""
+    if cache.dtype not in (torch.float16, torch.bfloat16):
+        raise TypeError("the unquantized K cache must be float16 or bfloat16")
+    p = _lib.KvPlane()
+    p.codes = cache.data_ptr()
+    p.scales = None
+    p.zeros = None
+    p.codes_stride = _stride3(cache)  # in 2-byte elements, as the C ABI expects for this mode
+    p.scales_stride = (C.c_int64 * 3)(0, 0, 0)
+    p.zeros_stride = (C.c_int64 * 3)(0, 0, 0)
+    p.mode = _lib.KV_F16 if cache.dtype == torch.float16 else _lib.KV_BF16
+    return p
+
+
+def kfp16_vint4_decode(
+    query: torch.Tensor,
+    key_cache_fp16: torch.Tensor,  # [num_blocks, block_size, kv_heads, head_size] fp16 / bf16
+    value_cache_int4: torch.Tensor,  # [num_blocks, block_size, kv_heads, head_size//2] uint8
+    v_scales: torch.Tensor,
+    block_table: torch.Tensor,
+    seq_lens: torch.Tensor,
+    num_kv_heads: int,
+    head_size: int,
+    block_n: int = 64,
+    v_zeros: Optional[torch.Tensor] = None,
+    asymmetric: bool = False,
+    *,
+    out_dtype: Optional[torch.dtype] = None,
+    max_seq_len: Optional[int] = None,
+    n_splits: Optional[int] = None,
+) -> torch.Tensor:
+    """K unquantized / V INT4 hybrid decode (reference :1159-1224).  Runs on the
+    stride-generic kernel (correct, not tuned)."""
+    _need_cuda(key_cache_fp16, value_cache_int4, v_scales, v_zeros)
+    kp = _fp_plane(key_cache_fp16)
+    vp = _plane(value_cache_int4, v_scales, v_zeros if asymmetric else None,
+                _int4_mode(asymmetric, v_zeros))
+    return _decode(query, kp, vp, key_cache_fp16.shape[0], block_table, seq_lens, num_kv_heads,
+                   head_size, key_cache_fp16.shape[1], out_dtype, max_seq_len, n_splits,
+                   False, True)
+
+
+def kfp16_vint8_decode(
+    query: torch.Tensor,
+    key_cache_fp16: torch.Tensor,
+    value_cache_int8: torch.Tensor,  # [num_blocks, block_size, kv_heads, head_size] int8
+    v_scales: torch.Tensor,
+    block_table: torch.Tensor,
+    seq_lens: torch.Tensor,
+    num_kv_heads: int,
+    head_size: int,
+    block_n: int = 64,
+    *,
+    out_dtype: Optional[torch.dtype] = None,
+    max_seq_len: Optional[int] = None,
+    n_splits: Optional[int] = None,
+) -> torch.Tensor:
+    """K unquantized / V INT8 hybrid decode (reference :1975-2028).  Stride-generic kernel."""
+    _need_cuda(key_cache_fp16, value_cache_int8, v_scales)
+    kp = _fp_plane(key_cache_fp16)
+    vp = _plane(value_cache_int8, v_scales, None, _lib.KV_INT8_G32)
+    return _decode(query, kp, vp, key_cache_fp16.shape[0], block_table, seq_lens, num_kv_heads,
+                   head_size, key_cache_fp16.shape[1], out_dtype, max_seq_len, n_splits,
+                   False, True)

@@ -235,8 +235,49 @@ def gen_v8_cases(m, out):
     out["v8_modes"] = rec
 
 
+def gen_kfp16_cases(m, out):
+    """Unquantized K: kfp16_vint4_decode (:1159-1224) and kfp16_vint8_decode (:1975-2028) on
+    the inputs of the decode cases (read back from their files).  The K cache holds the
+    keys in the query dtype (fp16 for the fp32 case); it is stored as an fp32 view."""
+    rec = {}
+    for name in ("decode_mha_f32_d64", "decode_gqa4_bf16_d128", "decode_gqa8_f16_d128"):
+        G = np.load(os.path.join(HERE, name + ".npz"))
+        dt = DT[str(G["q_dtype"])]
+        kdt = torch.float16 if dt == torch.float32 else dt
+        q = torch.from_numpy(G["query"]).to(dt)
+        k = torch.from_numpy(G["key"]).to(kdt)
+        v = torch.from_numpy(G["value"]).to(dt)
+        slots = torch.from_numpy(G["slot_mapping"])
+        bt = torch.from_numpy(G["block_table"])
+        seq_lens = torch.from_numpy(G["seq_lens"])
+        nb, P = int(G["num_blocks"]), int(G["block_size"])
+        hkv, d = int(G["num_kv_heads"]), int(G["head_size"])
+        kcache = torch.zeros(nb, P, hkv, d, dtype=kdt)
+        kcache.view(nb * P, hkv, d)[slots] = k
+        _, vc, _, vs, _, vz = alloc_cache(nb, P, hkv, d)
+        m.reshape_and_cache_v_only_int4(v, vc, vs, slots, vz, asymmetric=True)
+        o4 = m.kfp16_vint4_decode(q, kcache, vc, vs, bt, seq_lens, hkv, d, block_n=64,
+                                  v_zeros=vz, asymmetric=True)
+        vc8 = torch.zeros(nb, P, hkv, d, dtype=torch.int8)
+        vs8 = torch.zeros(nb, P, hkv, d // 32, dtype=torch.float16)
+        m.reshape_and_cache_v_int8(v, vc8, vs8, slots)
+        o8 = m.kfp16_vint8_decode(q, kcache, vc8, vs8, bt, seq_lens, hkv, d, block_n=64)
+        rec[name + "_kcache"] = kcache.float().numpy()
+        rec[name + "_kdtype"] = "f16" if kdt == torch.float16 else "bf16"
+        rec[name + "_kf16v4_out"] = o4.float().numpy()
+        rec[name + "_kf16v8_out"] = o8.float().numpy()
+        print("kfp16 decode", name, "done", flush=True)
+    out["kfp16_modes"] = rec
+
+
 def main():
     out = {}
+    if "--only-kfp16" in sys.argv:
+        gen_kfp16_cases(load_reference(), out)
+        for name, rec in out.items():
+            np.savez_compressed(os.path.join(HERE, name + ".npz"), **rec)
+            print("saved", name)
+        return
     if "--only-plugin" in sys.argv:
         gen_plugin_cases(out)
     elif "--only-v8" in sys.argv:
