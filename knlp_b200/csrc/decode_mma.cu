@@ -9,11 +9,13 @@
 // of its group.
 //
 // Data movement: each stage of the pipeline is TT tokens x HPB kv heads of
-// codes, scales and zeros, copied global -> shared with cp.async (16-byte
-// pieces for codes, whole scale/zero rows of 4 or 8 bytes), kStages deep.
-// Rows are stored warp-major in shared memory (the 16 rows a warp consumes are
-// contiguous) with an xor swizzle of the 16-byte column, so that both the
-// cp.async writes and the ldmatrix reads are bank-conflict free.
+// codes, scales and zeros (HPB <= 4 heads, one warp per head and 16-token tile),
+// copied global -> shared with cp.async in 16-byte pieces dealt in memory order,
+// three or four stages deep.  Code rows are stored warp-major in shared memory
+// (the 16 rows a warp consumes are contiguous) with an xor swizzle of the 16-byte
+// column, scale rows xor-permuted by their place in the bank period, so that the
+// cp.async writes, the ldmatrix reads and the scale loads are bank-conflict free.
+// While whole stages lie ahead the loop body carries no end-of-sequence test.
 //
 // Math: the per-token work is far too much for CUDA-core FMAs at HBM speed
 // (2 * n_rep * head_dim FMAs per 160 bytes), so both products run on the tensor
@@ -41,8 +43,12 @@
 // moves.  The partial written per (sequence, q head, split) is (m, l, o) with m
 // in the natural-log domain and o un-normalised.
 //
-// Nothing in this kernel waits on another CTA or on an mbarrier: the only
-// synchronisation is cp.async group completion and __syncthreads.
+// Synchronisation on the default path is cp.async group completion and
+// __syncthreads only; no CTA ever waits for another.  Two options go further: the TMA
+// staging waits on "stage landed" mbarriers of its own CTA, every wait bounded (a wait
+// that runs out sets g_decode_status and ends the CTA), and the single-launch finish
+// counts CTAs with an atomic, where the last one to arrive does the merge and nobody
+// waits.
 
 #include <cuda.h>
 
@@ -325,9 +331,9 @@ __device__ __forceinline__ bool run_stages(F& f, int it0, int n) {
   }
 }
 
-// TMA = true: stages are filled by cp.async.bulk.tensor copies issued by one warp
-// per iteration (the warps take turns) and handed over through full/empty
-// mbarriers; the warps never meet at a CTA barrier inside the main loop.
+// TMA = true: stages are filled by cp.async.bulk.tensor copies (one box per plane and
+// tile) and announced by a "stage landed" mbarrier; the warp that is last to finish
+// with a slot refills it; the warps never meet at a CTA barrier inside the main loop.
 // TMA = false: stages are filled by cp.async from all threads (any 16-byte
 // aligned strides), one __syncthreads per stage.
 template <int HD, int KMODE, int VMODE, bool SPLIT, bool TMA, int HPBL>

@@ -21,7 +21,9 @@ import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("KNLP_REFERENCE", "/root/reference")
+REF = os.environ.get("KNLP_REFERENCE")
+if not REF or not os.path.isdir(REF):
+    raise SystemExit("set KNLP_REFERENCE to a checkout of mcgrof/knlp")
 
 DT = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
 
