@@ -276,9 +276,12 @@ __device__ __forceinline__ void unpack_int8_pairs(uint32_t w, uint32_t out[2]) {
   out[1] = __byte_perm(u, 0u, 0x4341);
 }
 
-// Shared-memory geometry of a stage.  PAD = 16 (cp.async path) separates the 16-row
-// code tiles of the eight warps by one extra 16-byte piece, so that a warp-wide copy
-// of one token row (all heads, 512 contiguous bytes) lands in distinct banks.
+// Shared-memory geometry of a stage.  PAD (cp.async path: kTilePad = 64 bytes) separates
+// the 16-row code tiles of the warps.  A warp-wide copy of a token row scatters one 64-byte
+// run per head, i.e. per tile; with tiles half a 128-byte line apart the runs of two heads
+// complete one line between them.  Measured at 0 / 16 / 32 / 64 / 128 bytes: 962 / 962 /
+// 955 / 935 / 961 us on the headline shape, and 186 -> 150 us for the all-INT8 workload.
+constexpr int kTilePad = 64;
 template <int HD, int KMODE, int VMODE, int PAD>
 struct Geo {
   static constexpr bool kInt8K = (KMODE == KNLP_KV_INT8_G32);
@@ -339,7 +342,7 @@ __device__ __forceinline__ bool run_stages(F& f, int it0, int n) {
 template <int HD, int KMODE, int VMODE, bool SPLIT, bool TMA, int HPBL>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant__ TmaMaps tm) {
-  using G = Geo<HD, KMODE, VMODE, TMA ? 0 : 16>;
+  using G = Geo<HD, KMODE, VMODE, TMA ? 0 : kTilePad>;
   constexpr int kStages = G::kStages;
   constexpr bool kInt8V = G::kInt8V;
   constexpr int NG = G::NG;
@@ -547,7 +550,7 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
   // ---------------- cp.async path: copy role of this thread ----------------
   // The 16-byte pieces of a stage are dealt to the threads in MEMORY order (token,
   // then head, then piece), so a warp-wide cp.async reads 512 contiguous bytes (the
-  // natural layout keeps the heads of a token adjacent) and, thanks to the 16-byte pad
+  // natural layout keeps the heads of a token adjacent) and, thanks to the pad
   // between the warps' tiles, writes them to distinct banks.  Piece i of a plane:
   // token i / (HPB * CH), head (i / CH) % HPB, piece i % CH; a thread owns pieces
   // tid, tid + 256, ...  (same head and piece, tokens 256 / (HPB * CH) apart).
@@ -1545,7 +1548,7 @@ bool build_maps(const DecodeArgs& a, int hpb, TmaMaps* out) {
 
 template <int HD, int KMODE, int VMODE, bool SPLIT, bool TMA, int HPBL>
 int launch_hpb(const DecodeArgs& a, const MmaParams& mp, const TmaMaps& tm, cudaStream_t st) {
-  using G = Geo<HD, KMODE, VMODE, TMA ? 0 : 16>;
+  using G = Geo<HD, KMODE, VMODE, TMA ? 0 : kTilePad>;
   constexpr int kSmem = G::kSmemBytes + 1024;  // slack for the 1 KB alignment of the stages
   auto kern = decode_mma_kernel<HD, KMODE, VMODE, SPLIT, TMA, HPBL>;
   static int configured_dev = -1;  // per instantiation; the attribute is per device function
