@@ -417,6 +417,51 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_write_path(args):
+    """Side measurement, not the headline: the quantize-and-append kernel over a prefill-sized
+    batch (tokens x 8 kv heads x 128, bf16, K and V), algorithmic read + write bytes per
+    CUDA-event second.  One JSON line per quantizer."""
+    import torch
+    from knlp_b200 import ops, workloads
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    n, h, d, P = int((1 << 20) * args.scale), 8, 128, 16
+    g = torch.Generator(device=dev).manual_seed(1)
+    k = torch.randn(n, h, d, device=dev, generator=g).to(torch.bfloat16)
+    v = torch.randn(n, h, d, device=dev, generator=g).to(torch.bfloat16)
+    slots = torch.randperm(n, device=dev, generator=g).to(torch.int64)  # scattered pages
+    nb = (n + P - 1) // P
+    for mode, out_bytes in (("int4_asym", 160), ("int4_sym", 144), ("int8", 272)):
+        kc, vc, ks, vs, kz, vz = workloads.alloc_cache(nb, h, d, mode, mode, dev)
+        if mode == "int8":
+            def step():
+                ops.reshape_and_cache_k_int8(k, kc, ks, slots)
+                ops.reshape_and_cache_v_int8(v, vc, vs, slots)
+        else:
+            asym = mode == "int4_asym"
+            def step():
+                ops.reshape_and_cache_int4(k, v, kc, vc, ks, vs, slots, kz if asym else None,
+                                           vz if asym else None, asymmetric=asym)
+        for _ in range(max(args.warmup, 3)):
+            step()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        byts = n * h * (2 * d * 2 + out_bytes) + n * 8  # bf16 K and V in, codes/scales out, slots
+        hbm_gbs, peak_kind = peaks()
+        print(json.dumps({"write_path": mode, "tokens": n, "kv_heads": h, "head_dim": d,
+                          "src_dtype": "bf16", "ms_per_step": ms, "algorithmic_bytes": byts,
+                          "value": byts / ms / 1e9, "unit": "TB/s",
+                          "frac_of_hbm_peak": byts / ms / 1e6 / hbm_gbs, "peak": peak_kind,
+                          "note": "inputs 4.3 GB > L2; K and V quantized per step"}))
+        del kc, vc, ks, vs, kz, vz
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -434,8 +479,12 @@ def main():
                     help="how N > 1 GPUs split the work (default: kv heads, no exchange)")
     ap.add_argument("--profile", action="store_true",
                     help="short run for use under ncu: timed steps only, one JSON line of timings")
+    ap.add_argument("--write-path", action="store_true",
+                    help="time the quantize-and-append kernel instead (side measurement)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.write_path:
+        run_write_path(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
