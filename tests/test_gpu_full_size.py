@@ -132,3 +132,22 @@ def test_write_path_at_full_size(cuda_device):
         assert np.array_equal(rows(vs).view(np.uint16), ovs.reshape(len(sample), h, -1).view(np.uint16))
         del res, kc, vc, ks, vs, kz, vz
         torch.cuda.empty_cache()
+
+    # INT8 K and V: both kernels over the whole cache, sampled rows against the oracle
+    res = []
+    for kk, vv in ((k, v), (k_odd, v_odd)):
+        kc, vc = caches(d, torch.int8)
+        ks, vs, _, _ = scales()
+        ops.reshape_and_cache_k_int8(kk, kc, ks, slots)
+        ops.reshape_and_cache_v_int8(vv, vc, vs, slots)
+        res.append((kc, vc, ks, vs))
+    for a, b in zip(*res):
+        assert torch.equal(a, b), "wide and narrow INT8 kernels differ"
+    kc, vc, ks, vs = res[0]
+    okc = np.zeros((len(sample) // P, P, h, d), np.int8)
+    oks = np.zeros((len(sample) // P, P, h, d // 32), np.float16)
+    O.reshape_and_cache_k_int8(k[sample].float().cpu().numpy(), okc, oks, np.arange(len(sample)))
+    sl = slots[sample]
+    rows = lambda t: t.view(nb * P, h, -1)[sl].cpu().numpy()
+    assert np.array_equal(rows(kc), okc.reshape(len(sample), h, -1))
+    assert np.array_equal(rows(ks).view(np.uint16), oks.reshape(len(sample), h, -1).view(np.uint16))
