@@ -371,14 +371,21 @@ def run_ours(args):
         # read the pinned host buffers at every replay.
         eager_out = out_h.clone()
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            e2e_step()
-        out_h.zero_()
-        graph.replay()
-        torch.cuda.synchronize()
-        if not torch.equal(out_h, eager_out):
-            raise RuntimeError("graph replay of the end-to-end step differs from the eager step")
-        run_step, e2e_mode = graph.replay, "operator calls captured in one CUDA graph, replayed"
+        try:
+            # thread-local: CUDA calls of other threads (a process group's watchdog) are theirs
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                e2e_step()
+        except RuntimeError as exc:  # capture refused: the same calls run eagerly instead
+            graph = None
+            torch.cuda.synchronize()
+            e2e_mode = f"eager operator calls (graph capture failed: {str(exc)[:80]})"
+        if graph is not None:
+            out_h.zero_()
+            graph.replay()
+            torch.cuda.synchronize()
+            if not torch.equal(out_h, eager_out):
+                raise RuntimeError("graph replay of the end-to-end step differs from the eager step")
+            run_step, e2e_mode = graph.replay, "operator calls captured in one CUDA graph, replayed"
         for _ in range(3):
             run_step()
     barrier()
