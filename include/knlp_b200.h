@@ -1,11 +1,12 @@
 /*
  * knlp_b200 — C ABI of the B200 (sm_100a) packed-KV-cache hot path.
  *
- * Three device operations and their helpers:
- *   quant_append   quantize new K/V tokens and scatter them into the paged cache
- *   decode_splitk  split-context GQA decode attention over the packed cache,
- *                  emitting (m, l, o) softmax partials per (sequence, q head, split)
- *   combine        merge partials into the attention output (or into one partial)
+ * Device operations and their helpers:
+ *   quant_append      quantize new K/V tokens and scatter them into the paged cache
+ *   decode_attention  GQA decode attention over the packed cache, balanced inside one launch
+ *   decode_splitk     the same with a fixed split count, emitting (m, l, o) softmax
+ *                     partials per (sequence, q head, split)
+ *   combine           merge partials into the attention output (or into one partial)
  *
  * Every entry point is plain C: raw device pointers, sizes, strides and a
  * cudaStream_t passed as void*.  Nothing here allocates or synchronises except
@@ -14,11 +15,18 @@
  * capturable.  Return value: 0 on success, a negative
  * knlp_status on an argument error detected on the host before any launch.
  *
+ * Threads and devices: every entry point works on the CURRENT device of the calling
+ * thread and may be called from several host threads at once (the library's own
+ * per-device state is atomic or mutex-protected).  Calls that share a workspace,
+ * counters or a cache region they write must be ordered by the caller, as any two
+ * kernels on different streams.
+ *
  * Reference interfaces replaced (mcgrof/knlp, fused-quant/fused_int4.v0.1.0.py):
  *   reshape_and_cache_int4          :418-472   -> knlp_b200_quant_append
  *   reshape_and_cache_v_only_int4   :603-647   -> knlp_b200_quant_append (K plane NULL)
  *   reshape_and_cache_k_int8        :1287-1312 -> knlp_b200_quant_append (K mode INT8_G32)
- *   fused_int4_decode               :901-979   -> knlp_b200_decode_splitk + knlp_b200_combine
+ *   fused_int4_decode               :901-979   -> knlp_b200_decode_attention
+ *                                                 (or knlp_b200_decode_splitk + knlp_b200_combine)
  *   kint8_vint4_decode              :1496-1554 -> same, K mode INT8_G32
  *   reshape_and_cache_v_int8        :1619-1645 -> knlp_b200_quant_append (V mode INT8_G32)
  *   kint8_vint8_decode              :1796-1843 -> decode entry points, both modes INT8_G32
@@ -37,7 +45,7 @@
 extern "C" {
 #endif
 
-#define KNLP_B200_ABI_VERSION 1
+#define KNLP_B200_ABI_VERSION 2
 #define KNLP_GROUP_SIZE 32
 
 typedef enum {
@@ -145,8 +153,11 @@ int knlp_b200_decode_plan(int n_seqs, int n_q_heads, int n_kv_heads, int head_di
  *                [0, num_blocks) before use, so a corrupt table cannot fault
  *   n_splits     >= 1.  Split i of a sequence covers tokens
  *                [i*chunk, min((i+1)*chunk, seq_len)), chunk = ceil(max_seq_len/n_splits)
- *                rounded up to a multiple of 64
- *   max_seq_len  upper bound of seq_lens known on the host (sizes the splits)
+ *                rounded up to a multiple of 64; the LAST split runs on to seq_len
+ *   max_seq_len  bound of seq_lens known on the host.  It only sizes the splits: a
+ *                sequence longer than it is still attended to in full (its last split
+ *                is then longer than the others), so a bound given too small costs
+ *                balance, never tokens
  *   part_m/l     float [n_seqs, n_q_heads, n_splits]   running max (natural-log domain,
  *                of the scaled scores) and sum of exp(s - m); empty split: -inf, 0
  *   part_o       float [n_seqs, n_q_heads, n_splits, head_dim]  UN-normalised sum p*v
@@ -162,27 +173,48 @@ int knlp_b200_decode_splitk(const void* query, int q_dtype, const int64_t q_stri
                             unsigned flags, void* stream);
 
 /*
- * Decode attention in ONE launch: knlp_b200_decode_splitk whose CTAs also merge the
- * splits (the CTA that finishes a sequence's group of kv heads last does it), i.e. the
- * whole of fused_int4_decode / kint8_vint4_decode (reference :901-979, :1496-1554).
- * Arguments as knlp_b200_decode_splitk (the partials workspace is still needed; part_o
- * must be 16-byte aligned here), plus
- *   counters     int32 [n_seqs * n_kv_heads] (an upper bound of what is used: one per
- *                sequence and group of kv heads that a CTA covers), all ZERO on entry; the kernel
- *                leaves them zero, so one buffer zeroed once serves every later call on
- *                the same stream (calls that may overlap need separate buffers)
- *   out          [n_seqs * n_q_heads, head_dim] of out_dtype, row stride out_row_stride
- *                elements: normalised attention output, 0 for sequences without tokens
- * Layouts that only the stride-generic kernel can address are finished with the
- * combine kernel instead; the result is the same.
+ * Workspace of knlp_b200_decode_attention for a decode shape: the number of floats and of
+ * int32 counters it needs (host arithmetic; queries the SM count of the current device).
+ * Both depend only on the arguments given here, so a caller sizes them once for its
+ * largest batch.
  */
+int knlp_b200_decode_workspace(int n_seqs, int n_q_heads, int n_kv_heads, int head_dim,
+                               int block_size, int max_seq_len, int64_t* workspace_floats_out,
+                               int64_t* counter_ints_out);
+
+/*
+ * Decode attention, the whole of fused_int4_decode / kint8_vint4_decode / kint8_vint8_decode
+ * (reference :901-979, :1496-1554, :1796-1843): query and packed cache in, attention
+ * output out.  Arguments as knlp_b200_decode_splitk, without a split count: the work is
+ * balanced inside the launch (a persistent grid; the CTAs that serve one sequence and
+ * block of kv heads share its tokens through a ticket counter and the one that finishes
+ * last merges their partial softmax states).  One kernel launch for ordinary batches; a
+ * second, dependent launch merges when one sequence is spread over most of the machine.
+ *   workspace    floats, >= what knlp_b200_decode_workspace reports; contents are scratch
+ *   counters     int32, >= what knlp_b200_decode_workspace reports, all ZERO on entry; the
+ *                kernel leaves them zero, so one buffer zeroed once serves every later
+ *                call on the same stream, whatever its shape (calls that may overlap on
+ *                the GPU need separate workspace and counters)
+ *   out          [n_seqs * n_q_heads, head_dim] of out_dtype, row stride out_row_stride
+ *                elements: normalised attention output, 0 for sequences without tokens.
+ *                With KNLP_DECODE_EMIT_PARTIAL: float rows of head_dim + 2 values
+ *                [o un-normalised, m, l] (row stride out_row_stride >= head_dim + 2),
+ *                the buffer a rank of a context shard sends in its one all-gather
+ *   max_seq_len  host-known bound of seq_lens; sizes the grid only
+ * Layouts that the tensor-core kernels cannot address (and the flags FORCE_GENERIC,
+ * USE_TMA, FIXED_SPLITS) run knlp_b200_decode_splitk + knlp_b200_combine inside the same
+ * workspace instead; the result is the same.
+ */
+#define KNLP_DECODE_EMIT_PARTIAL 4u /* out receives the merged partial, not the output */
+#define KNLP_DECODE_FIXED_SPLITS 8u /* use the split-context kernel + combine */
 int knlp_b200_decode_attention(const void* query, int q_dtype, const int64_t q_stride[2],
                                const knlp_kv_plane* k_plane, const knlp_kv_plane* v_plane,
                                const int32_t* block_table, int64_t bt_stride,
                                const int32_t* seq_lens, int64_t num_blocks,
                                int n_seqs, int n_q_heads, int n_kv_heads, int head_dim,
-                               int block_size, int n_splits, int max_seq_len,
-                               float* part_m, float* part_l, float* part_o, int32_t* counters,
+                               int block_size, int max_seq_len,
+                               float* workspace, int64_t workspace_floats,
+                               int32_t* counters, int64_t counter_ints,
                                void* out, int out_dtype, int64_t out_row_stride,
                                unsigned flags, void* stream);
 

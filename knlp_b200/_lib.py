@@ -13,7 +13,7 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 # KNLP_B200_LIB points the binding at another build of the same library.
 LIB_PATH = os.environ.get("KNLP_B200_LIB") or os.path.join(_PKG, "libknlp_b200.so")
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 # dtype / mode codes of include/knlp_b200.h
 F32, F16, BF16 = 0, 1, 2
@@ -21,6 +21,8 @@ KV_NONE, KV_INT4_SYM, KV_INT4_ASYM, KV_INT8_G32 = 0, 1, 2, 3
 KV_F16, KV_BF16 = 4, 5  # unquantized K plane of the kfp16_* decodes
 DECODE_FORCE_GENERIC = 1
 DECODE_USE_TMA = 2
+DECODE_EMIT_PARTIAL = 4
+DECODE_FIXED_SPLITS = 8
 
 SYMBOLS = (
     "knlp_b200_abi_version",
@@ -30,6 +32,7 @@ SYMBOLS = (
     "knlp_b200_decode_plan",
     "knlp_b200_decode_splitk",
     "knlp_b200_decode_attention",
+    "knlp_b200_decode_workspace",
     "knlp_b200_combine",
     "knlp_b200_decode_noalloc",
     "knlp_b200_plugin_quantize",
@@ -92,9 +95,13 @@ def load() -> C.CDLL:
     lib.knlp_b200_decode_attention.restype = C.c_int
     lib.knlp_b200_decode_attention.argtypes = [
         C.c_void_p, C.c_int, I64P, PL, PL, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
-        C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
-        C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64,
+        C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+        C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int, C.c_int64,
         C.c_uint, C.c_void_p]
+    lib.knlp_b200_decode_workspace.restype = C.c_int
+    lib.knlp_b200_decode_workspace.argtypes = [
+        C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+        C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
     lib.knlp_b200_combine.restype = C.c_int
     lib.knlp_b200_combine.argtypes = [
         C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_int64, C.c_int64,

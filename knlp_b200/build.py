@@ -3,13 +3,14 @@
     python -m knlp_b200.build [--force] [--verbose]
 
 No GPU is needed to build.  Objects go to knlp_b200/csrc/build/, the library to
-knlp_b200/libknlp_b200.so.  A file is recompiled when it or a header is newer
-than its object.
+knlp_b200/libknlp_b200.so.  A file is recompiled when it or a header it includes is newer
+than its object (headers are found by following the #include "..." lines).
 """
 
 from __future__ import annotations
 
 import os
+import re
 import shutil
 import subprocess
 import sys
@@ -39,23 +40,38 @@ def _sources():
     return sorted(f for f in os.listdir(CSRC) if f.endswith(".cu"))
 
 
-def _headers_mtime() -> float:
-    paths = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
-    paths += [os.path.join(INCLUDE, f) for f in os.listdir(INCLUDE)]
-    return max(os.path.getmtime(p) for p in paths)
+_INC = re.compile(r'^\s*#\s*include\s+"([^"]+)"', re.M)
+
+
+def _deps_mtime(path: str, seen=None) -> float:
+    """Newest modification time of a source file and the local headers it includes."""
+    seen = set() if seen is None else seen
+    path = os.path.normpath(path)
+    if path in seen or not os.path.exists(path):
+        return 0.0
+    seen.add(path)
+    t = os.path.getmtime(path)
+    with open(path) as f:
+        text = f.read()
+    for inc in _INC.findall(text):
+        for base in (os.path.dirname(path), INCLUDE):
+            cand = os.path.join(base, inc)
+            if os.path.exists(cand):
+                t = max(t, _deps_mtime(cand, seen))
+                break
+    return t
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(OBJ, exist_ok=True)
     nvcc = _nvcc()
-    hdr = _headers_mtime()
     jobs = []
     objs = []
     for src in _sources():
         s = os.path.join(CSRC, src)
         o = os.path.join(OBJ, src[:-3] + ".o")
         objs.append(o)
-        if force or not os.path.exists(o) or os.path.getmtime(o) < max(os.path.getmtime(s), hdr):
+        if force or not os.path.exists(o) or os.path.getmtime(o) < _deps_mtime(s):
             cmd = [nvcc, *ARCH, *COMMON, *EXTRA.get(src, []), "-c", s, "-o", o]
             if verbose:
                 cmd.insert(1, "-Xptxas")

@@ -1,7 +1,7 @@
 // C ABI of the library: argument validation and dispatch.  No exceptions, no
 // C++ types and no allocation cross this boundary.
 
-#include <mutex>
+#include <atomic>
 
 #include "common.cuh"
 
@@ -35,20 +35,23 @@ int check_plane(const knlp_kv_plane* p, bool unquantized_k) {
   return KNLP_OK;
 }
 
+// SM count of the CURRENT device, looked up once per device index.
 int sm_count() {
-  static int cached = 0;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    int dev = 0, n = 0;
-    if (cudaGetDevice(&dev) == cudaSuccess &&
-        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) {
-      cached = n;
-    } else {
-      cudaGetLastError();
-      cached = 148;  // B200
-    }
-  });
-  return cached;
+  constexpr int kMaxDevices = 64;
+  static std::atomic<int> cached[kMaxDevices];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    cudaGetLastError();
+    return 148;  // B200
+  }
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (n > 0) return n;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+    cudaGetLastError();
+    n = 148;
+  }
+  cached[dev].store(n, std::memory_order_relaxed);
+  return n;
 }
 
 }  // namespace
@@ -122,7 +125,7 @@ int knlp_b200_decode_plan(int n_seqs, int n_q_heads, int n_kv_heads, int head_di
   const int64_t base = static_cast<int64_t>(n_seqs) * (n_kv_heads / hpb);
   const int64_t slots = static_cast<int64_t>(kDecodeCtasPerSm) * sm_count();
   const int max_splits = max_seq_len >= 512 ? (max_seq_len / 256 > 1024 ? 1024 : max_seq_len / 256) : 1;
-  // Cost model (microseconds, coarse, measured on B200): a wave of CTAs costs a fixed
+  // Cost model (microseconds, coarse): a wave of CTAs costs a fixed
   // set-up plus 1.2 us per stage (16 tokens x the CTA's heads) of its split; merging costs a
   // little per split.  Fewer, longer splits amortise the set-up; more splits fill the
   // machine and even out ragged batches.
@@ -151,29 +154,26 @@ int knlp_b200_decode_plan(int n_seqs, int n_q_heads, int n_kv_heads, int head_di
 
 namespace {
 
-// Shared body of the two decode entry points.  out == nullptr: partials only.
-int decode_common(const void* query, int q_dtype, const int64_t q_stride[2],
-                  const knlp_kv_plane* k_plane, const knlp_kv_plane* v_plane,
-                  const int32_t* block_table, int64_t bt_stride, const int32_t* seq_lens,
-                  int64_t num_blocks, int n_seqs, int n_q_heads, int n_kv_heads, int head_dim,
-                  int block_size, int n_splits, int max_seq_len, float* part_m, float* part_l,
-                  float* part_o, int* counters, void* out, int out_dtype,
-                  int64_t out_row_stride, unsigned flags, void* stream) {
-  if (!query || !q_stride || !block_table || !seq_lens || !part_m || !part_l || !part_o)
-    return KNLP_ERR_NULL;
+// Argument checks and DecodeArgs shared by the decode entry points.  Returns 1 when
+// there is nothing to do (no sequences).
+int decode_args(const void* query, int q_dtype, const int64_t q_stride[2],
+                const knlp_kv_plane* k_plane, const knlp_kv_plane* v_plane,
+                const int32_t* block_table, int64_t bt_stride, const int32_t* seq_lens,
+                int64_t num_blocks, int n_seqs, int n_q_heads, int n_kv_heads, int head_dim,
+                int block_size, int max_seq_len, DecodeArgs* out) {
+  if (!query || !q_stride || !block_table || !seq_lens) return KNLP_ERR_NULL;
   if (!dtype_ok(q_dtype)) return KNLP_ERR_DTYPE;
   if (n_seqs < 0 || n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads)
     return KNLP_ERR_SHAPE;
   if (!head_dim_ok(head_dim) || block_size <= 0 || num_blocks <= 0) return KNLP_ERR_SHAPE;
   if (n_seqs > 65535 || n_kv_heads * ((n_q_heads / n_kv_heads + 7) / 8) > 65535)
     return KNLP_ERR_SHAPE;
-  if (n_splits < 1 || max_seq_len < 0) return KNLP_ERR_WORKSPACE;
+  if (max_seq_len < 0) return KNLP_ERR_WORKSPACE;
   int rc = check_plane(k_plane, true);
   if (rc) return rc;
   rc = check_plane(v_plane, false);
   if (rc) return rc;
-  if (n_seqs == 0) return KNLP_OK;
-
+  if (n_seqs == 0) return 1;
   DecodeArgs a{};
   a.q = query;
   a.q_dtype = q_dtype;
@@ -190,29 +190,18 @@ int decode_common(const void* query, int q_dtype, const int64_t q_stride[2],
   a.n_kv_heads = n_kv_heads;
   a.head_dim = head_dim;
   a.block_size = block_size;
-  a.n_splits = n_splits;
-  a.chunk = split_chunk(max_seq_len, n_splits);
-  a.part_m = part_m;
-  a.part_l = part_l;
-  a.part_o = part_o;
-  // the kernel merges the splits itself only while they are few (kFuseMaxSplits)
-  const bool fuse = out != nullptr && n_splits <= kFuseMaxSplits;
-  a.out = fuse ? out : nullptr;
-  a.out_dtype = out_dtype;
-  a.out_row_stride = out_row_stride;
-  a.counters = counters;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  rc = 1;
+  *out = a;
+  return KNLP_OK;
+}
+
+// Split-context launch: tensor-core kernel where the layout allows, else the generic one.
+int launch_splitk(const DecodeArgs& a, unsigned flags, cudaStream_t st) {
+  int rc = 1;
   if (!(flags & KNLP_DECODE_FORCE_GENERIC)) {
     rc = launch_decode_mma(a, (flags & KNLP_DECODE_USE_TMA) != 0, st);
-    if (rc < 0 || (rc == 0 && (fuse || !out))) return rc;  // done, or failed for good
+    if (rc <= 0) return rc;  // launched, or failed for good
   }
-  if (rc == 1) rc = launch_decode_generic(a, st);
-  if (rc != KNLP_OK || !out) return rc;
-  // many splits, or the stride-generic kernel: merge with the combine kernel
-  return launch_combine(part_m, part_l, part_o, n_splits, n_splits, 1,
-                        static_cast<int64_t>(n_splits) * head_dim, head_dim, out, out_dtype,
-                        out_row_stride, nullptr, nullptr, 0, n_seqs * n_q_heads, head_dim, st);
+  return launch_decode_generic(a, st);
 }
 
 }  // namespace
@@ -226,10 +215,36 @@ int knlp_b200_decode_splitk(const void* query, int q_dtype, const int64_t q_stri
                             int n_q_heads, int n_kv_heads, int head_dim, int block_size,
                             int n_splits, int max_seq_len, float* part_m, float* part_l,
                             float* part_o, unsigned flags, void* stream) {
-  return decode_common(query, q_dtype, q_stride, k_plane, v_plane, block_table, bt_stride,
-                       seq_lens, num_blocks, n_seqs, n_q_heads, n_kv_heads, head_dim, block_size,
-                       n_splits, max_seq_len, part_m, part_l, part_o, nullptr, nullptr, KNLP_F32,
-                       0, flags, stream);
+  if (!part_m || !part_l || !part_o) return KNLP_ERR_NULL;
+  if (n_splits < 1) return KNLP_ERR_WORKSPACE;
+  DecodeArgs a;
+  const int rc = decode_args(query, q_dtype, q_stride, k_plane, v_plane, block_table, bt_stride,
+                             seq_lens, num_blocks, n_seqs, n_q_heads, n_kv_heads, head_dim,
+                             block_size, max_seq_len, &a);
+  if (rc) return rc < 0 ? rc : KNLP_OK;
+  a.n_splits = n_splits;
+  a.chunk = split_chunk(max_seq_len, n_splits);
+  a.part_m = part_m;
+  a.part_l = part_l;
+  a.part_o = part_o;
+  return launch_splitk(a, flags, static_cast<cudaStream_t>(stream));
+}
+
+int knlp_b200_decode_workspace(int n_seqs, int n_q_heads, int n_kv_heads, int head_dim,
+                               int block_size, int max_seq_len, int64_t* workspace_floats_out,
+                               int64_t* counter_ints_out) {
+  if (!workspace_floats_out || !counter_ints_out) return KNLP_ERR_NULL;
+  int n_splits = 1;
+  int64_t split_floats = 0;
+  const int rc = knlp_b200_decode_plan(n_seqs > 0 ? n_seqs : 1, n_q_heads, n_kv_heads, head_dim,
+                                       block_size, max_seq_len, 0, 0, &n_splits, &split_floats);
+  if (rc) return rc;
+  int64_t dq_floats = 0, dq_ints = 0;
+  dq_workspace_size(n_seqs > 0 ? n_seqs : 1, n_q_heads, n_kv_heads, head_dim, sm_count(),
+                    &dq_floats, &dq_ints);
+  *workspace_floats_out = (dq_floats > split_floats ? dq_floats : split_floats) + 4;
+  *counter_ints_out = dq_ints;
+  return KNLP_OK;
 }
 
 int knlp_b200_decode_attention(const void* query, int q_dtype, const int64_t q_stride[2],
@@ -237,16 +252,56 @@ int knlp_b200_decode_attention(const void* query, int q_dtype, const int64_t q_s
                                const int32_t* block_table, int64_t bt_stride,
                                const int32_t* seq_lens, int64_t num_blocks, int n_seqs,
                                int n_q_heads, int n_kv_heads, int head_dim, int block_size,
-                               int n_splits, int max_seq_len, float* part_m, float* part_l,
-                               float* part_o, int32_t* counters, void* out, int out_dtype,
+                               int max_seq_len, float* workspace, int64_t workspace_floats,
+                               int32_t* counters, int64_t counter_ints, void* out, int out_dtype,
                                int64_t out_row_stride, unsigned flags, void* stream) {
-  if (!out || !counters) return KNLP_ERR_NULL;
+  if (!out || !workspace || !counters) return KNLP_ERR_NULL;
   if (!dtype_ok(out_dtype)) return KNLP_ERR_DTYPE;
-  if (reinterpret_cast<uintptr_t>(part_o) % 16) return KNLP_ERR_STRIDE;  // merged as float4
-  return decode_common(query, q_dtype, q_stride, k_plane, v_plane, block_table, bt_stride,
+  const bool emit = (flags & KNLP_DECODE_EMIT_PARTIAL) != 0;
+  if (emit && out_dtype != KNLP_F32) return KNLP_ERR_DTYPE;
+  DecodeArgs a;
+  int rc = decode_args(query, q_dtype, q_stride, k_plane, v_plane, block_table, bt_stride,
                        seq_lens, num_blocks, n_seqs, n_q_heads, n_kv_heads, head_dim, block_size,
-                       n_splits, max_seq_len, part_m, part_l, part_o, counters, out, out_dtype,
-                       out_row_stride, flags, stream);
+                       max_seq_len, &a);
+  if (rc) return rc < 0 ? rc : KNLP_OK;
+  a.out = out;
+  a.out_dtype = out_dtype;
+  a.out_row_stride = out_row_stride;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // the merge reads the partial outputs as float4
+  const uintptr_t mis = reinterpret_cast<uintptr_t>(workspace) % 16;
+  if (mis % 4) return KNLP_ERR_STRIDE;
+  if (mis) {
+    workspace += (16 - mis) / 4;
+    workspace_floats -= (16 - mis) / 4;
+  }
+  if (!(flags & (KNLP_DECODE_FORCE_GENERIC | KNLP_DECODE_USE_TMA | KNLP_DECODE_FIXED_SPLITS))) {
+    rc = launch_decode_dq(a, workspace, workspace_floats, counters, counter_ints, max_seq_len, emit,
+                          sm_count(), st);
+    if (rc <= 0) return rc;  // launched, or failed for good
+  }
+  // fixed splits: split-context kernel into the workspace, then the combine kernel
+  int n_splits = 1;
+  int64_t need = 0;
+  rc = knlp_b200_decode_plan(n_seqs, n_q_heads, n_kv_heads, head_dim, block_size, max_seq_len,
+                             k_plane->mode, v_plane->mode, &n_splits, &need);
+  if (rc) return rc;
+  if (need > workspace_floats) return KNLP_ERR_WORKSPACE;
+  const int64_t rows = static_cast<int64_t>(n_seqs) * n_q_heads;
+  a.n_splits = n_splits;
+  a.chunk = split_chunk(max_seq_len, n_splits);
+  a.part_o = workspace;
+  a.part_m = workspace + rows * n_splits * head_dim;
+  a.part_l = a.part_m + rows * n_splits;
+  a.out = nullptr;
+  rc = launch_splitk(a, flags, st);
+  if (rc != KNLP_OK) return rc;
+  float* fo = static_cast<float*>(out);
+  return launch_combine(a.part_m, a.part_l, a.part_o, n_splits, n_splits, 1,
+                        static_cast<int64_t>(n_splits) * head_dim, head_dim, out, out_dtype,
+                        out_row_stride, emit ? fo + head_dim : nullptr,
+                        emit ? fo + head_dim + 1 : nullptr, out_row_stride,
+                        static_cast<int>(rows), head_dim, st);
 }
 
 int knlp_b200_combine(const float* part_m, const float* part_l, const float* part_o,

@@ -88,7 +88,104 @@ combine_kernel(const float* __restrict__ pm, const float* __restrict__ pl,
   }
 }
 
+// Merge of the balanced decode kernel's partial slots.  The parts of a pair are
+// consecutive slots of `heads` rows each; pair_info holds (first slot, parts) per pair.
+// Grid (row, 32-element slice of the head): with one long sequence spread over the whole
+// machine a row has hundreds of parts, and the slices give the merge enough CTAs.  The
+// kernel is launched as a programmatic dependent of the decode kernel: it may become
+// resident while that one drains and waits here for its memory to be complete.
+__global__ void __launch_bounds__(kThreads)
+combine_pairs_kernel(const float* __restrict__ ws_m, const float* __restrict__ ws_l,
+                     const float* __restrict__ ws_o, const int* __restrict__ pair_info,
+                     int heads, int head_dim, void* out, int out_dtype, int64_t out_row,
+                     int emit_partial) {
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
+  const int row = blockIdx.x;
+  const int pair = row / heads, r = row % heads;
+  const int e = blockIdx.y * 32 + (threadIdx.x & 31);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int slot0 = pair_info[2 * pair];
+  const int parts = pair_info[2 * pair + 1];
+  const float* rm = ws_m + static_cast<int64_t>(slot0) * heads + r;
+  const float* rl = ws_l + static_cast<int64_t>(slot0) * heads + r;
+  const float* ro = ws_o + (static_cast<int64_t>(slot0) * heads + r) * head_dim + e;
+  const int64_t o_part = static_cast<int64_t>(heads) * head_dim;
+
+  __shared__ float s_red[kWarps];
+  __shared__ float s_l[kWarps];
+  __shared__ float s_o[kWarps][32];
+
+  float m = -INFINITY;
+  for (int p = threadIdx.x; p < parts; p += kThreads)
+    if (rl[p * heads] > 0.0f) m = fmaxf(m, rm[p * heads]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if (lane == 0) s_red[warp] = m;
+  __syncthreads();
+  m = s_red[0];
+#pragma unroll
+  for (int w = 1; w < kWarps; ++w) m = fmaxf(m, s_red[w]);
+
+  float l = 0.0f, acc = 0.0f;
+#pragma unroll 4
+  for (int p = warp; p < parts; p += kWarps) {
+    const float lp = rl[p * heads];
+    if (lp > 0.0f) {
+      const float w = __expf(rm[p * heads] - m);
+      l = fmaf(lp, w, l);
+      acc = fmaf(ro[p * o_part], w, acc);
+    }
+  }
+  if (lane == 0) s_l[warp] = l;
+  s_o[warp][lane] = acc;
+  __syncthreads();
+  if (warp == 0) {
+    float lt = 0.0f, ot = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      lt += s_l[w];
+      ot += s_o[w][lane];
+    }
+    if (emit_partial) {
+      float* orow = static_cast<float*>(out) + row * out_row;
+      orow[e] = ot;
+      if (e == 0) {
+        orow[head_dim] = m;
+        orow[head_dim + 1] = lt;
+      }
+    } else {
+      store_elem_rt(out, row * out_row + e, lt > 0.0f ? ot / lt : 0.0f, out_dtype);
+    }
+  }
+}
+
 }  // namespace
+
+int launch_combine_pairs(const float* ws_m, const float* ws_l, const float* ws_o,
+                         const int* pair_info, int heads, int n_rows, int head_dim, void* out,
+                         int out_dtype, int64_t out_row, bool emit_partial, cudaStream_t st) {
+  if (n_rows == 0) return KNLP_OK;
+  if (head_dim % 32) return KNLP_ERR_SHAPE;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(n_rows, head_dim / 32);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const int emit = emit_partial ? 1 : 0;
+  const cudaError_t rc =
+      cudaLaunchKernelEx(&cfg, combine_pairs_kernel, ws_m, ws_l, ws_o, pair_info, heads, head_dim,
+                         out, out_dtype, out_row, emit);
+  if (rc != cudaSuccess) {
+    cudaGetLastError();
+    return KNLP_ERR_LAUNCH;
+  }
+  return KNLP_OK;
+}
 
 int launch_combine(const float* pm, const float* pl, const float* po, int n_parts,
                    int64_t ml_row, int64_t ml_part, int64_t o_row, int64_t o_part, void* out,

@@ -100,12 +100,10 @@ struct DecodeArgs {
   float* part_m;
   float* part_l;
   float* part_o;
-  // Fused finish (tensor-core kernel only; out == nullptr: partials only).  counters:
-  // one int per (sequence, head block of the launch), zero on entry and left zero.
+  // Output of the balanced one-launch kernel (the split-context kernels write partials)
   void* out;
   int out_dtype;
   int64_t out_row_stride;
-  int* counters;
 };
 
 int launch_decode_generic(const DecodeArgs& a, cudaStream_t st);
@@ -113,20 +111,25 @@ int launch_decode_generic(const DecodeArgs& a, cudaStream_t st);
 // tensor-core kernel (caller falls back to the generic one), <0 on error.
 // allow_tma = false keeps the tensor-core kernel on its cp.async loader.
 int launch_decode_mma(const DecodeArgs& a, bool allow_tma, cudaStream_t st);
+// Shape / layout test of the tensor-core kernels: 0 = eligible (heads per CTA and page
+// size filled in as log2), 1 = generic kernel only.
+int decode_mma_layout(const DecodeArgs& a, int* hpb_log2, int* page_log2);
 
-// CTA shape of the tensor-core decode kernel, shared with the split planner: one warp
+// CTA shape of the tensor-core decode kernels, shared with the split planner: one warp
 // per (kv head, 16-token tile), so a CTA covers at most kDecodeWarps kv heads; sixteen
-// warps of ~128 registers fit on an SM.  Four CTAs of four warps measured faster than
-// two of eight (the CTAs of an SM wait at their stage barriers independently).
-#ifndef KNLP_WARPS
-#define KNLP_WARPS 4
-#endif
-constexpr int kDecodeWarps = KNLP_WARPS;  // 8, 4 or 2
-// The fused finish of the decode kernel merges the splits of a row group in ONE CTA:
-// worth it (it saves a launch and a pass) while the splits are few, a serial tail when
-// they are many.  Beyond this many splits the merge goes to the combine kernel.
-constexpr int kFuseMaxSplits = 64;
+// warps of ~128 registers fit on an SM, as four CTAs of four warps (the CTAs of an SM
+// wait at their stage barriers independently).
+constexpr int kDecodeWarps = 4;
 constexpr int kDecodeCtasPerSm = 16 / kDecodeWarps;
+
+// Balanced one-launch decode (decode_dq_kernel.cuh): a.out receives the attention output
+// (emit_partial: fp32 rows [o un-normalised, m, l]).  ws / ints: the workspace sized by
+// dq_workspace_size; the ints are counters that must be zero on entry and are left zero.  Returns KNLP_OK, 1 if the call is not eligible (nothing launched),
+// <0 on error.
+int launch_decode_dq(const DecodeArgs& a, float* ws, int64_t ws_floats, int* ints, int64_t n_ints,
+                     int max_seq_len, bool emit_partial, int n_sms, cudaStream_t st);
+void dq_workspace_size(int n_seqs, int n_q_heads, int n_kv_heads, int head_dim, int n_sms,
+                       int64_t* floats, int64_t* ints);
 // Device-side status word of the decode kernels (0 = clean); synchronises.
 int read_and_clear_decode_status();
 
@@ -134,5 +137,11 @@ int launch_combine(const float* pm, const float* pl, const float* po, int n_part
                    int64_t ml_row, int64_t ml_part, int64_t o_row, int64_t o_part, void* out,
                    int out_dtype, int64_t out_row, float* out_m, float* out_l, int64_t out_ml,
                    int n_rows, int head_dim, cudaStream_t st);
+// Merge of the balanced kernel's partial slots: row r of pair p = slots
+// pair_info[2p] .. + pair_info[2p+1] - 1 (heads rows each).  Launched as a programmatic
+// dependent of the kernel before it on the stream.
+int launch_combine_pairs(const float* ws_m, const float* ws_l, const float* ws_o,
+                         const int* pair_info, int heads, int n_rows, int head_dim, void* out,
+                         int out_dtype, int64_t out_row, bool emit_partial, cudaStream_t st);
 
 }  // namespace knlp

@@ -1,0 +1,7 @@
+// Instantiations of the balanced one-launch decode kernel for one K/V mode pair.
+#include "decode_dq_kernel.cuh"
+
+namespace knlp {
+template int launch_dq_pair<KNLP_KV_INT4_ASYM, KNLP_KV_INT4_ASYM>(const DecodeArgs&, const DqParams&, bool, cudaStream_t);
+template int dq_chunk_of_pair<KNLP_KV_INT4_ASYM, KNLP_KV_INT4_ASYM>(int, int);
+}  // namespace knlp

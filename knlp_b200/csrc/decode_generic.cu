@@ -65,7 +65,7 @@ decode_generic_kernel(const DecodeArgs a, int n_rep, int q_groups) {
   int seq_len = a.seq_lens[seq];
   if (seq_len < 0) seq_len = 0;
   const int start = split * a.chunk;
-  const int end = min(start + a.chunk, seq_len);
+  const int end = split == a.n_splits - 1 ? seq_len : min(start + a.chunk, seq_len);
 
   // q heads handled here: kvh*n_rep + qg*QH + [0, QH), masked to n_rep
   const int h_first = qg * QH;

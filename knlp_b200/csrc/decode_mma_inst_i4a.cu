@@ -1,0 +1,7 @@
+// Instantiations of the split-context tensor-core decode kernel for one K/V mode pair.
+#include "decode_mma_kernel.cuh"
+
+namespace knlp {
+template int launch_mma_pair<KNLP_KV_INT4_ASYM, KNLP_KV_INT4_ASYM>(const DecodeArgs&, const MmaParams&, bool,
+                                       const TmaMaps*, cudaStream_t);
+}  // namespace knlp

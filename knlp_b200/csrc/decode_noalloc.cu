@@ -61,6 +61,9 @@ int knlp_b200_decode_noalloc(const void* query, int q_dtype, const int64_t q_str
                              int n_splits, int max_seq_len, void* out, int out_dtype,
                              int64_t out_row_stride, void* stream) {
   if (!out) return KNLP_ERR_NULL;
+  // everything the merge would reject is rejected here, before the decode kernel is enqueued
+  if (out_dtype != KNLP_F32 && out_dtype != KNLP_F16 && out_dtype != KNLP_BF16)
+    return KNLP_ERR_DTYPE;
   if (n_seqs < 0 || n_q_heads <= 0 || head_dim <= 0) return KNLP_ERR_SHAPE;
   if (n_seqs == 0) return KNLP_OK;
   const long long rows = static_cast<long long>(n_seqs) * n_q_heads;

@@ -362,27 +362,36 @@ def combine_packed(gathered: torch.Tensor, out_dtype=torch.float32) -> torch.Ten
     return out
 
 
-_counters = {}  # (device index, stream) -> zeroed int32 buffer the fused kernel leaves zero
+_workspaces = {}  # (device index, stream) -> (float workspace, int32 counters left zero)
 
 
-def _counter_buffer(dev: torch.device, n: int) -> torch.Tensor:
+def _decode_workspace(dev: torch.device, S: int, Hq: int, Hkv: int, d: int, block_size: int,
+                      max_seq_len: int):
+    """Workspace of ``knlp_b200_decode_attention`` for the current stream: grown on demand,
+    reused by every later call on that stream (calls on one stream are ordered)."""
+    nf, ni = C.c_int64(0), C.c_int64(0)
+    rc = _lib.load().knlp_b200_decode_workspace(S, Hq, Hkv, d, block_size, max_seq_len,
+                                                C.byref(nf), C.byref(ni))
+    _lib.check(rc, "knlp_b200_decode_workspace")
     key = (dev.index, _stream(dev))
-    buf = _counters.get(key)
-    if buf is None or buf.numel() < n:
-        buf = torch.zeros(max(n, 4096), dtype=torch.int32, device=dev)
-        _counters[key] = buf
-    return buf
+    cur = _workspaces.get(key)
+    if cur is None or cur[0].numel() < nf.value or cur[1].numel() < ni.value:
+        cur = (torch.empty(max(nf.value, 1 << 20), dtype=torch.float32, device=dev),
+               torch.zeros(max(ni.value, 4096), dtype=torch.int32, device=dev))
+        _workspaces[key] = cur
+    return cur
 
 
 def decode_attention(
     query: torch.Tensor, k_plane: _lib.KvPlane, v_plane: _lib.KvPlane, num_blocks: int,
     block_table: torch.Tensor, seq_lens: torch.Tensor, num_kv_heads: int, head_size: int,
     block_size: int, *, out_dtype=None, max_seq_len: Optional[int] = None,
-    n_splits: Optional[int] = None, force_generic=False,
+    emit_partial: bool = False, out: Optional[torch.Tensor] = None, flags: int = 0,
 ) -> torch.Tensor:
-    """Split-context decode and the merge of the splits in ONE kernel launch
-    (``knlp_b200_decode_attention``).  Returns [S, Hq, d] in ``out_dtype`` (default:
-    the query's)."""
+    """Decode attention balanced inside one launch (``knlp_b200_decode_attention``).
+    Returns [S, Hq, d] in ``out_dtype`` (default: the query's); with ``emit_partial`` the
+    merged softmax partial per row instead, fp32 [S, Hq, d + 2] = [o un-normalised, m, l]
+    (what a rank of a context shard all-gathers)."""
     dev = _need_cuda(query, block_table, seq_lens)
     if block_table.dtype != torch.int32 or seq_lens.dtype != torch.int32:
         raise TypeError("block_table and seq_lens must be int32")
@@ -394,32 +403,33 @@ def decode_attention(
         raise ValueError("query shape does not match num_kv_heads / head_size")
     if max_seq_len is None:
         max_seq_len = block_table.shape[1] * block_size
-    if n_splits is None:
-        n_splits = plan_splits(S, Hq, num_kv_heads, head_size, block_size, max_seq_len)
-    ws = torch.empty((S * Hq * n_splits * (d + 2),), dtype=torch.float32, device=dev)
-    n_ml = S * Hq * n_splits
-    out = torch.empty((S, Hq, d), dtype=query.dtype if out_dtype is None else out_dtype, device=dev)
-    counters = _counter_buffer(dev, S * num_kv_heads)
-    base = ws.data_ptr()
+    ws, counters = _decode_workspace(dev, S, Hq, num_kv_heads, d, block_size, max_seq_len)
+    if emit_partial:
+        if out is None:
+            out = torch.empty((S, Hq, d + 2), dtype=torch.float32, device=dev)
+        flags |= _lib.DECODE_EMIT_PARTIAL
+    elif out is None:
+        out = torch.empty((S, Hq, d), dtype=query.dtype if out_dtype is None else out_dtype,
+                          device=dev)
+    if not out.is_contiguous():
+        raise ValueError("out must be contiguous")
     with torch.cuda.device(dev):
         rc = _lib.load().knlp_b200_decode_attention(
             query.data_ptr(), _dt(query), _stride2(query), C.byref(k_plane), C.byref(v_plane),
             block_table.data_ptr(), block_table.stride(0), seq_lens.data_ptr(), num_blocks,
-            S, Hq, num_kv_heads, head_size, block_size, n_splits, max_seq_len,
-            # o first: the kernel's merge reads it as float4 (16-byte aligned), m and l behind
-            base + 4 * n_ml * d, base + 4 * n_ml * (d + 1), base, counters.data_ptr(),
-            out.data_ptr(), _DT[out.dtype], d, _decode_flags(force_generic), _stream(dev))
+            S, Hq, num_kv_heads, head_size, block_size, max_seq_len,
+            ws.data_ptr(), ws.numel(), counters.data_ptr(), counters.numel(),
+            out.data_ptr(), _DT[out.dtype], out.shape[-1], flags, _stream(dev))
     _lib.check(rc, "knlp_b200_decode_attention")
     return out
 
 
 def _decode(query, k_plane, v_plane, num_blocks, block_table, seq_lens, num_kv_heads,
             head_size, block_size, out_dtype, max_seq_len, n_splits, force_generic,
-            two_launches=True):
-    # Default: the split-context kernel, then the combine kernel.  The single-launch
-    # form (the decode kernel's last CTA per row group merges the splits) measured 1-3 %
-    # slower at every benchmark shape and is kept selectable (two_launches=False).
-    if two_launches:
+            two_launches=False):
+    # Default: the balanced one-launch kernel.  A given split count, a forced kernel or
+    # two_launches=True run the split-context kernel and the combine kernel instead.
+    if two_launches or n_splits is not None or force_generic:
         pm, pl, po = decode_partials(query, k_plane, v_plane, num_blocks, block_table, seq_lens,
                                      num_kv_heads, head_size, block_size,
                                      max_seq_len=max_seq_len, n_splits=n_splits,
@@ -428,8 +438,7 @@ def _decode(query, k_plane, v_plane, num_blocks, block_table, seq_lens, num_kv_h
                                 out_dtype=query.dtype if out_dtype is None else out_dtype)
     return decode_attention(query, k_plane, v_plane, num_blocks, block_table, seq_lens,
                             num_kv_heads, head_size, block_size, out_dtype=out_dtype,
-                            max_seq_len=max_seq_len, n_splits=n_splits,
-                            force_generic=force_generic)
+                            max_seq_len=max_seq_len)
 
 
 def fused_int4_decode(
@@ -451,7 +460,7 @@ def fused_int4_decode(
     max_seq_len: Optional[int] = None,
     n_splits: Optional[int] = None,
     force_generic: bool = False,
-    two_launches: bool = True,
+    two_launches: bool = False,
 ) -> torch.Tensor:
     """Decode attention over the packed INT4 cache (reference :901-979).
 
@@ -486,7 +495,7 @@ def kint8_vint4_decode(
     max_seq_len: Optional[int] = None,
     n_splits: Optional[int] = None,
     force_generic: bool = False,
-    two_launches: bool = True,
+    two_launches: bool = False,
 ) -> torch.Tensor:
     """K INT8 (group-32 scales) / V INT4 decode attention (reference :1496-1554)."""
     _need_cuda(key_cache_int8, value_cache_int4, k_scales, v_scales, v_zeros)
@@ -514,7 +523,7 @@ def kint8_vint8_decode(
     max_seq_len: Optional[int] = None,
     n_splits: Optional[int] = None,
     force_generic: bool = False,
-    two_launches: bool = True,
+    two_launches: bool = False,
 ) -> torch.Tensor:
     """K INT8 / V INT8 decode attention, group-32 scales on both (reference :1796-1843)."""
     _need_cuda(key_cache_int8, value_cache_int8, k_scales, v_scales)
@@ -565,7 +574,7 @@ def kfp16_vint4_decode(
                 _int4_mode(asymmetric, v_zeros))
     return _decode(query, kp, vp, key_cache_fp16.shape[0], block_table, seq_lens, num_kv_heads,
                    head_size, key_cache_fp16.shape[1], out_dtype, max_seq_len, n_splits,
-                   False, True)
+                   False, False)
 
 
 def kfp16_vint8_decode(
@@ -589,4 +598,4 @@ def kfp16_vint8_decode(
     vp = _plane(value_cache_int8, v_scales, None, _lib.KV_INT8_G32)
     return _decode(query, kp, vp, key_cache_fp16.shape[0], block_table, seq_lens, num_kv_heads,
                    head_size, key_cache_fp16.shape[1], out_dtype, max_seq_len, n_splits,
-                   False, True)
+                   False, False)

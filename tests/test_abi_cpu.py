@@ -34,7 +34,7 @@ def test_every_declared_symbol_is_exported(lib):
 
 
 def test_abi_version_and_strerror(lib):
-    assert lib.knlp_b200_abi_version() == 1
+    assert lib.knlp_b200_abi_version() == 2
     assert lib.knlp_b200_strerror(0) == b"ok"
     for code in range(-9, 0):
         assert len(lib.knlp_b200_strerror(code)) > 3
