@@ -100,6 +100,137 @@ __device__ __forceinline__ void load_q_groups(const void* base, int64_t row, int
   }
 }
 
+// Merge of the partials of one pair by the CTA that arrived last: out[row] = sum_p w_p o_p
+// with w_p = l_p e^(m_p - m) / sum_q l_q e^(m_q - m).  pm, pl: [parts][heads]; po: [parts]
+// [heads][HD]; sw: shared-memory scratch of sw_floats floats; s_mrow, s_irow: MAXH floats
+// of shared memory.  Kept out of line so that its registers are not the main loop's.
+template <int HD, int MAXH>
+__device__ __noinline__ void merge_pair(const float* pm, const float* pl, const float* po,
+                                        const int parts, const int heads, float* sw,
+                                        const int sw_floats, float* s_mrow, float* s_irow,
+                                        void* out, const int out_dtype,
+                                        const int64_t out_row_stride, const int64_t row0,
+                                        const int emit_partial) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tile = min(parts, sw_floats / heads);
+  const bool one_pass = parts <= 32 && parts <= tile;
+  {
+    constexpr int kRowsW = MAXH / kWarpsCta;
+    float rm[kRowsW], rl[kRowsW], lp[kRowsW], mp[kRowsW];
+#pragma unroll
+    for (int k = 0; k < kRowsW; ++k) {
+      rm[k] = -INFINITY;
+      rl[k] = 0.0f;
+    }
+    for (int p0 = 0; p0 < parts; p0 += 32) {
+#pragma unroll
+      for (int k = 0; k < kRowsW; ++k) {
+        const int r = warp + k * kWarpsCta;
+        const bool valid = r < heads && p0 + lane < parts;
+        lp[k] = valid ? __ldcg(pl + (p0 + lane) * heads + r) : 0.0f;
+        mp[k] = valid ? __ldcg(pm + (p0 + lane) * heads + r) : -INFINITY;
+      }
+#pragma unroll
+      for (int k = 0; k < kRowsW; ++k) {
+        float mx = lp[k] > 0.0f ? mp[k] : -INFINITY;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        const float m_new = fmaxf(rm[k], mx);
+        float sum = lp[k] > 0.0f ? lp[k] * __expf(mp[k] - m_new) : 0.0f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        rl[k] = (rl[k] > 0.0f ? rl[k] * __expf(rm[k] - m_new) : 0.0f) + sum;
+        rm[k] = m_new;
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < kRowsW; ++k) {
+      const int r = warp + k * kWarpsCta;
+      const float inv = emit_partial ? 1.0f : (rl[k] > 0.0f ? 1.0f / rl[k] : 0.0f);
+      if (one_pass && r < heads && lane < parts)
+        sw[r * tile + lane] = lp[k] > 0.0f ? __expf(mp[k] - rm[k]) * inv : 0.0f;
+      if (lane == 0 && r < heads) {
+        s_mrow[r] = rm[k];
+        s_irow[r] = inv;
+        if (emit_partial) {
+          float* orow = static_cast<float*>(out) + (row0 + r) * out_row_stride;
+          orow[HD] = rm[k];
+          orow[HD + 1] = rl[k];
+        }
+      }
+    }
+  }
+  __syncthreads();
+  // (2) out[row] = sum_p w_p o_p.  A thread owns up to kItems (row, four elements) items
+  // and keeps their sums; the partial outputs are fetched kBatch parts of every item at
+  // a time, all those loads independent of each other.
+  constexpr int kVec = HD / 4;
+  constexpr int kItems = (MAXH * kVec + kThreads - 1) / kThreads;
+  constexpr int kBatch = kItems >= 16 ? 1 : 16 / kItems;
+  const float4* po4 = reinterpret_cast<const float4*>(po);
+  float4 acc[kItems];
+#pragma unroll
+  for (int k = 0; k < kItems; ++k) acc[k] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  for (int p0 = 0; p0 < parts; p0 += tile) {
+    const int np = min(tile, parts - p0);
+    if (!one_pass) {
+      __syncthreads();  // the previous tile's weights are no longer read
+      for (int i = tid; i < heads * np; i += kThreads) {
+        const int r = i / np, p = p0 + i % np;
+        const float l1 = __ldcg(pl + p * heads + r);
+        sw[r * tile + (p - p0)] =
+            l1 > 0.0f ? __expf(__ldcg(pm + p * heads + r) - s_mrow[r]) * s_irow[r] : 0.0f;
+      }
+      __syncthreads();
+    }
+    for (int pb = 0; pb < np; pb += kBatch) {
+      float4 v[kItems][kBatch];
+#pragma unroll
+      for (int k = 0; k < kItems; ++k) {
+        const int i = tid + k * kThreads;
+        const int r = i / kVec, e4 = i % kVec;
+#pragma unroll
+        for (int q = 0; q < kBatch; ++q) {
+          // a member that saw no token wrote zeros, so no value needs skipping
+          const bool valid = i < heads * kVec && pb + q < np;
+          v[k][q] = valid ? __ldcg(po4 + (static_cast<int64_t>(p0 + pb + q) * heads + r) * kVec + e4)
+                          : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < kItems; ++k) {
+        const int i = tid + k * kThreads;
+        const int r = min(i / kVec, heads - 1);
+#pragma unroll
+        for (int q = 0; q < kBatch; ++q) {
+          const float wgt = pb + q < np ? sw[r * tile + pb + q] : 0.0f;
+          acc[k].x = fmaf(v[k][q].x, wgt, acc[k].x);
+          acc[k].y = fmaf(v[k][q].y, wgt, acc[k].y);
+          acc[k].z = fmaf(v[k][q].z, wgt, acc[k].z);
+          acc[k].w = fmaf(v[k][q].w, wgt, acc[k].w);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < kItems; ++k) {
+    const int i = tid + k * kThreads;
+    if (i < heads * kVec) {
+      const int r = i / kVec, e4 = i % kVec;
+      const int64_t o = (row0 + r) * out_row_stride + 4 * e4;
+      if (emit_partial) {
+        float* orow = static_cast<float*>(out) + o;
+        orow[0] = acc[k].x; orow[1] = acc[k].y; orow[2] = acc[k].z; orow[3] = acc[k].w;
+      } else {
+        store_elem_rt(out, o, acc[k].x, out_dtype);
+        store_elem_rt(out, o + 1, acc[k].y, out_dtype);
+        store_elem_rt(out, o + 2, acc[k].z, out_dtype);
+        store_elem_rt(out, o + 3, acc[k].w, out_dtype);
+      }
+    }
+  }
+}
+
 template <int HD, int KMODE, int VMODE, bool SPLIT, int HPBL>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
@@ -1020,116 +1151,13 @@ decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
     __syncthreads();
     if (!dp.fuse || !s_last) return;
     __threadfence();
-    // (1) maximum and normalisation of every row over the parts: a warp owns the rows
-    // warp, warp + 4, ...; a lane reads one part of each of them, all loads in flight together
-    const float* pm = dp.ws_m + static_cast<int64_t>(first_slot) * heads;
-    const float* pl = dp.ws_l + static_cast<int64_t>(first_slot) * heads;
-    const int64_t row0 = static_cast<int64_t>(seq) * a.n_q_heads + hb * heads;
-    {
-      constexpr int kRowsW = HPB * 8 / kWarpsCta;
-      float rm[kRowsW], rl[kRowsW];
-#pragma unroll
-      for (int k = 0; k < kRowsW; ++k) {
-        rm[k] = -INFINITY;
-        rl[k] = 0.0f;
-      }
-      for (int p0 = 0; p0 < parts; p0 += 32) {
-        float lp[kRowsW], mp[kRowsW];
-#pragma unroll
-        for (int k = 0; k < kRowsW; ++k) {
-          const int r = warp + k * kWarpsCta;
-          const bool valid = r < heads && p0 + lane < parts;
-          lp[k] = valid ? __ldcg(pl + (p0 + lane) * heads + r) : 0.0f;
-          mp[k] = valid ? __ldcg(pm + (p0 + lane) * heads + r) : -INFINITY;
-        }
-#pragma unroll
-        for (int k = 0; k < kRowsW; ++k) {
-          float mx = lp[k] > 0.0f ? mp[k] : -INFINITY;
-#pragma unroll
-          for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-          const float m_new = fmaxf(rm[k], mx);
-          float sum = lp[k] > 0.0f ? lp[k] * __expf(mp[k] - m_new) : 0.0f;
-#pragma unroll
-          for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-          rl[k] = (rl[k] > 0.0f ? rl[k] * __expf(rm[k] - m_new) : 0.0f) + sum;
-          rm[k] = m_new;
-        }
-      }
-#pragma unroll
-      for (int k = 0; k < kRowsW; ++k) {
-        const int r = warp + k * kWarpsCta;
-        if (lane == 0 && r < heads) {
-          s_mrow[r] = rm[k];
-          s_irow[r] = dp.emit_partial ? 1.0f : (rl[k] > 0.0f ? 1.0f / rl[k] : 0.0f);
-          if (dp.emit_partial) {
-            float* orow = static_cast<float*>(a.out) + (row0 + r) * a.out_row_stride;
-            orow[HD] = rm[k];
-            orow[HD + 1] = rl[k];
-          }
-        }
-      }
-    }
-    __syncthreads();
-    // (2) out[row] = sum_p w_p o_p.  The weights of a tile of parts go to shared memory
-    // first (the stage buffers are free), so that the loads of the partial outputs are
-    // independent of each other and many are in flight; a thread owns up to kItems
-    // (row, four elements) items and keeps their sums over the tiles.
-    constexpr int kVec = HD / 4;
-    constexpr int kItems = (HPB * 8 * kVec + kThreads - 1) / kThreads;
-    float* sw = reinterpret_cast<float*>(smem);  // [heads][tile]
-    const int tile = min(parts, static_cast<int>(G::kSmemBytes / 4) / heads);
-    const float4* po4 =
-        reinterpret_cast<const float4*>(dp.ws_o + static_cast<int64_t>(first_slot) * heads * HD);
-    float4 acc[kItems];
-#pragma unroll
-    for (int k = 0; k < kItems; ++k) acc[k] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    for (int p0 = 0; p0 < parts; p0 += tile) {
-      const int np = min(tile, parts - p0);
-      __syncthreads();  // the previous tile's weights are no longer read
-      for (int i = tid; i < heads * np; i += kThreads) {
-        const int r = i / np, p = p0 + i % np;
-        const float lp = __ldcg(pl + p * heads + r);
-        sw[r * tile + (p - p0)] =
-            lp > 0.0f ? __expf(__ldcg(pm + p * heads + r) - s_mrow[r]) * s_irow[r] : 0.0f;
-      }
-      __syncthreads();
-#pragma unroll
-      for (int k = 0; k < kItems; ++k) {
-        const int i = tid + k * kThreads;
-        if (i < heads * kVec) {
-          const int r = i / kVec, e4 = i % kVec;
-          const float4* src = po4 + (static_cast<int64_t>(p0) * heads + r) * kVec + e4;
-          const float* wr = sw + r * tile;
-#pragma unroll 8
-          for (int p = 0; p < np; ++p) {
-            // a member that saw no token wrote zeros, so no value needs skipping
-            const float4 v = __ldcg(src + static_cast<int64_t>(p) * heads * kVec);
-            const float wgt = wr[p];
-            acc[k].x = fmaf(v.x, wgt, acc[k].x);
-            acc[k].y = fmaf(v.y, wgt, acc[k].y);
-            acc[k].z = fmaf(v.z, wgt, acc[k].z);
-            acc[k].w = fmaf(v.w, wgt, acc[k].w);
-          }
-        }
-      }
-    }
-#pragma unroll
-    for (int k = 0; k < kItems; ++k) {
-      const int i = tid + k * kThreads;
-      if (i < heads * kVec) {
-        const int r = i / kVec, e4 = i % kVec;
-        const int64_t o = (row0 + r) * a.out_row_stride + 4 * e4;
-        if (dp.emit_partial) {
-          float* orow = static_cast<float*>(a.out) + o;
-          orow[0] = acc[k].x; orow[1] = acc[k].y; orow[2] = acc[k].z; orow[3] = acc[k].w;
-        } else {
-          store_elem_rt(a.out, o, acc[k].x, a.out_dtype);
-          store_elem_rt(a.out, o + 1, acc[k].y, a.out_dtype);
-          store_elem_rt(a.out, o + 2, acc[k].z, a.out_dtype);
-          store_elem_rt(a.out, o + 3, acc[k].w, a.out_dtype);
-        }
-      }
-    }
+    merge_pair<HD, HPB * 8>(dp.ws_m + static_cast<int64_t>(first_slot) * heads,
+                            dp.ws_l + static_cast<int64_t>(first_slot) * heads,
+                            dp.ws_o + static_cast<int64_t>(first_slot) * heads * HD, parts, heads,
+                            reinterpret_cast<float*>(smem), static_cast<int>(G::kSmemBytes / 4),
+                            s_mrow, s_irow, a.out, a.out_dtype, a.out_row_stride,
+                            static_cast<int64_t>(seq) * a.n_q_heads + hb * heads,
+                            dp.emit_partial);
   };
 
   // ---------------- the pairs this CTA's share touches ----------------
