@@ -482,76 +482,6 @@ decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
     }
     int taken = (home || quota >= 2) ? 2 : 1;  // thread 0: chunks drawn or owned so far
 
-    // ---------------- q fragments (B operand), kept in registers ----------------
-    // B column n = fr.  SPLIT: head n/2, part n%2 (hi, lo); else head n.
-    uint32_t bq[NG][2][2];
-    float qsum[NG][2];
-    {
-      const int col = fr;
-      const int head = SPLIT ? (col >> 1) : col;
-      const bool lo_part = SPLIT && (col & 1);
-      const bool live = head < n_rep;
-      const int qh = kvh * n_rep + (live ? head : 0);
-      const int64_t qbase = static_cast<int64_t>(seq) * a.q_stride[0] + qh * a.q_stride[1];
-      float xq[NG][8];
-      // slot e of group g is element 32g + 8ft + e (INT4 K) or 32g + 16(e>>2) + 4ft + (e&3)
-      if (live) {
-        load_q_groups<NG, kInt8K>(a.q, qbase, ft, a.q_dtype, xq);
-      } else {
-#pragma unroll
-        for (int g = 0; g < NG; ++g)
-#pragma unroll
-          for (int e = 0; e < 8; ++e) xq[g][e] = 0.0f;
-      }
-      float colsum[NG];
-#pragma unroll
-      for (int g = 0; g < NG; ++g) {
-        __half v[8];
-        float s = 0.0f;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          float x = xq[g][e];
-          float wgt = 1.0f;
-          if constexpr (!kInt8K) {
-            // the A operand holds, per byte, the even nibble alone and the whole byte (even
-            // + 16 * odd): the even slot takes q_e - q_o / 16, the odd slot q_o / 16 (with q
-            // as a single fp16 the nibbles are isolated and only the odd slot is scaled)
-            if (e & 1) {
-              x *= 0.0625f;
-              if constexpr (SPLIT) wgt = 17.0f; else wgt = 16.0f;
-            } else if constexpr (SPLIT) {
-              x -= xq[g][e + 1] * 0.0625f;
-            }
-          }
-          __half h = __float2half_rn(x);
-          if (lo_part) h = __float2half_rn(x - __half2float(h));
-          s += wgt * __half2float(h);
-          v[e] = h;
-        }
-        colsum[g] = s;
-        if constexpr (kInt8K) {
-          bq[g][0][0] = pack_h2(v[0], v[1]);
-          bq[g][0][1] = pack_h2(v[2], v[3]);
-          bq[g][1][0] = pack_h2(v[4], v[5]);
-          bq[g][1][1] = pack_h2(v[6], v[7]);
-        } else {
-          bq[g][0][0] = pack_h2(v[0], v[4]);
-          bq[g][0][1] = pack_h2(v[1], v[5]);
-          bq[g][1][0] = pack_h2(v[2], v[6]);
-          bq[g][1][1] = pack_h2(v[3], v[7]);
-        }
-      }
-#pragma unroll
-      for (int g = 0; g < NG; ++g) {
-        float s = colsum[g];
-        s += __shfl_xor_sync(0xffffffffu, s, 1);
-        s += __shfl_xor_sync(0xffffffffu, s, 2);
-        qsum[g][0] = __shfl_sync(0xffffffffu, s, (2 * ft) * 4) * kTwoM24;
-        qsum[g][1] = __shfl_sync(0xffffffffu, s, (2 * ft + 1) * 4) * kTwoM24;
-        if constexpr (SPLIT) qsum[g][0] += qsum[g][1];
-      }
-    }
-
     // source pointers of this thread's pieces in block 0 (at token tt % 16 of the block)
     const uint8_t* k_pp[kKPer];
     const uint8_t* v_pp[kVPer];
@@ -694,6 +624,77 @@ decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
         return true;
       };
       run_stages<0, kStages - 1, false>(first_fill, 0, kStages);
+    }
+
+    // ---------------- q fragments (B operand), kept in registers ----------------
+    // (built while the first copies are in flight)
+    // B column n = fr.  SPLIT: head n/2, part n%2 (hi, lo); else head n.
+    uint32_t bq[NG][2][2];
+    float qsum[NG][2];
+    {
+      const int col = fr;
+      const int head = SPLIT ? (col >> 1) : col;
+      const bool lo_part = SPLIT && (col & 1);
+      const bool live = head < n_rep;
+      const int qh = kvh * n_rep + (live ? head : 0);
+      const int64_t qbase = static_cast<int64_t>(seq) * a.q_stride[0] + qh * a.q_stride[1];
+      float xq[NG][8];
+      // slot e of group g is element 32g + 8ft + e (INT4 K) or 32g + 16(e>>2) + 4ft + (e&3)
+      if (live) {
+        load_q_groups<NG, kInt8K>(a.q, qbase, ft, a.q_dtype, xq);
+      } else {
+#pragma unroll
+        for (int g = 0; g < NG; ++g)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) xq[g][e] = 0.0f;
+      }
+      float colsum[NG];
+#pragma unroll
+      for (int g = 0; g < NG; ++g) {
+        __half v[8];
+        float s = 0.0f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          float x = xq[g][e];
+          float wgt = 1.0f;
+          if constexpr (!kInt8K) {
+            // the A operand holds, per byte, the even nibble alone and the whole byte (even
+            // + 16 * odd): the even slot takes q_e - q_o / 16, the odd slot q_o / 16 (with q
+            // as a single fp16 the nibbles are isolated and only the odd slot is scaled)
+            if (e & 1) {
+              x *= 0.0625f;
+              if constexpr (SPLIT) wgt = 17.0f; else wgt = 16.0f;
+            } else if constexpr (SPLIT) {
+              x -= xq[g][e + 1] * 0.0625f;
+            }
+          }
+          __half h = __float2half_rn(x);
+          if (lo_part) h = __float2half_rn(x - __half2float(h));
+          s += wgt * __half2float(h);
+          v[e] = h;
+        }
+        colsum[g] = s;
+        if constexpr (kInt8K) {
+          bq[g][0][0] = pack_h2(v[0], v[1]);
+          bq[g][0][1] = pack_h2(v[2], v[3]);
+          bq[g][1][0] = pack_h2(v[4], v[5]);
+          bq[g][1][1] = pack_h2(v[6], v[7]);
+        } else {
+          bq[g][0][0] = pack_h2(v[0], v[4]);
+          bq[g][0][1] = pack_h2(v[1], v[5]);
+          bq[g][1][0] = pack_h2(v[2], v[6]);
+          bq[g][1][1] = pack_h2(v[3], v[7]);
+        }
+      }
+#pragma unroll
+      for (int g = 0; g < NG; ++g) {
+        float s = colsum[g];
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        s += __shfl_xor_sync(0xffffffffu, s, 2);
+        qsum[g][0] = __shfl_sync(0xffffffffu, s, (2 * ft) * 4) * kTwoM24;
+        qsum[g][1] = __shfl_sync(0xffffffffu, s, (2 * ft + 1) * 4) * kTwoM24;
+        if constexpr (SPLIT) qsum[g][0] += qsum[g][1];
+      }
     }
 
     // One iteration consumes stage kS of the chunk of round R and refills the slot freed
