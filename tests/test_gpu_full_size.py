@@ -34,7 +34,12 @@ def test_decode_at_full_size(cuda_device):
     n_rep = w.n_q_heads // w.n_kv_heads
     out = w.decode(out_dtype=torch.float32)
     assert torch.isfinite(out).all()
-    assert torch.equal(out, w.decode(out_dtype=torch.float32))  # deterministic
+    # The balanced kernel hands chunks out dynamically: the order of summation, and with it
+    # the last bits, may differ between runs.  The fixed-split path is bitwise repeatable.
+    _close(w.decode(out_dtype=torch.float32).cpu().numpy(), out.cpu().numpy(), "rerun")
+    fixed = w.decode(out_dtype=torch.float32, two_launches=True)
+    assert torch.equal(fixed, w.decode(out_dtype=torch.float32, two_launches=True))
+    _close(fixed.cpu().numpy(), out.cpu().numpy(), "balanced vs fixed splits")
 
     # sampled rows against the oracle over the whole context
     pages = 131072 // 16
