@@ -135,6 +135,17 @@ def _quant_append(key, value, k_plane, v_plane, slot_mapping, head_size, block_s
     _lib.check(rc, "knlp_b200_quant_append")
 
 
+def quant_append(key, value, k_plane, v_plane, slot_mapping, block_size: int,
+                 clip_ratio: Optional[float] = None) -> None:
+    """Quantize new tokens into both cache planes in ONE launch, whatever their modes (the
+    reference needs two calls when K and V differ: reshape_and_cache_k_int8 :1287-1312 and
+    reshape_and_cache_v_only_int4 :603-647).  Planes as built by ``_plane``; ``key`` /
+    ``value`` [num_tokens, num_kv_heads, head_size]; either side may be None."""
+    src = key if key is not None else value
+    _quant_append(key, value, k_plane, v_plane, slot_mapping, src.shape[2], block_size,
+                  OUTLIER_CLIP_RATIO if clip_ratio is None else clip_ratio)
+
+
 def reshape_and_cache_int4(
     key: torch.Tensor,  # [num_tokens, num_heads, head_size]
     value: torch.Tensor,
@@ -380,6 +391,16 @@ def _decode_workspace(dev: torch.device, S: int, Hq: int, Hkv: int, d: int, bloc
                torch.zeros(max(ni.value, 4096), dtype=torch.int32, device=dev))
         _workspaces[key] = cur
     return cur
+
+
+def decode_workspace_floats(S: int, Hq: int, Hkv: int, d: int, block_size: int,
+                            max_seq_len: int) -> int:
+    """Floats of scratch ``knlp_b200_decode_attention`` asks for at this shape."""
+    nf, ni = C.c_int64(0), C.c_int64(0)
+    rc = _lib.load().knlp_b200_decode_workspace(S, Hq, Hkv, d, block_size, max_seq_len,
+                                                C.byref(nf), C.byref(ni))
+    _lib.check(rc, "knlp_b200_decode_workspace")
+    return nf.value
 
 
 def decode_attention(

@@ -15,10 +15,10 @@ kv-head shard
 
 context shard
     Rank r owns tokens [r*T/G, (r+1)*T/G) of every sequence (page aligned).  It
-    runs the split-context kernel over its segment, merges its own splits into
-    ONE partial per (sequence, q head), packed as fp32 rows [o(d), m, l]; a single
-    all-gather (NCCL over NVLink) moves S*Hq*(d+2)*4 bytes per rank; every rank
-    then merges the G partials with the combine kernel.
+    runs the decode kernel over its segment, which leaves ONE partial per
+    (sequence, q head), packed as fp32 rows [o(d), m, l], in the send buffer; a
+    single all-gather (NCCL over NVLink) moves S*Hq*(d+2)*4 bytes per rank; every
+    rank then merges the G partials with the combine kernel.
 
 The plumbing here (ownership arithmetic, the all-gather) is device agnostic so
 that it can be tested with gloo ranks on CPU; the kernels are CUDA only.
@@ -99,6 +99,23 @@ def gather_heads(out_slice: torch.Tensor, group=None) -> torch.Tensor:
         dist.all_gather(list(buf.unbind(0)), out_slice, group=group)
     S, hq, d = out_slice.shape
     return buf.permute(1, 0, 2, 3).reshape(S, world * hq, d)
+
+
+def context_sharded_attention(query, k_plane, v_plane, num_blocks, block_table, local_seq_lens,
+                              num_kv_heads: int, head_size: int, block_size: int, *,
+                              max_seq_len=None, group=None, out_dtype=None) -> torch.Tensor:
+    """One decode step of a context shard on CUDA: this rank's segment of every sequence is
+    attended to by the balanced kernel, which writes the rank's ONE packed softmax partial
+    per (sequence, q head) straight into the buffer that the all-gather sends (the only
+    exchange of the step); the merge of the ranks' partials follows.  ``block_table`` and
+    ``local_seq_lens`` describe the rank's own segment.  Returns [S, Hq, d] on every rank."""
+    from . import ops
+    packed = ops.decode_attention(query, k_plane, v_plane, num_blocks, block_table,
+                                  local_seq_lens, num_kv_heads, head_size, block_size,
+                                  max_seq_len=max_seq_len, emit_partial=True)
+    gathered = all_gather_packed(packed, group)
+    return ops.combine_packed(gathered,
+                              out_dtype=query.dtype if out_dtype is None else out_dtype)
 
 
 def context_sharded_decode(local_partials, group=None, out_dtype=torch.float32) -> torch.Tensor:

@@ -60,6 +60,27 @@ class Workload:
         pages = sum((L + PAGE - 1) // PAGE for L in self.seq_lens_host)
         return toks * self.n_kv_heads * self.kv_bytes_per_token_head() + qo + 4 * pages
 
+    def planes(self):
+        """The (K, V) cache planes as the C ABI takes them."""
+        L = ops._lib
+        if self.k_mode == "int8":
+            kp = ops._plane(self.key_cache, self.k_scales, None, L.KV_INT8_G32)
+        else:
+            asym = self.k_mode == "int4_asym"
+            kp = ops._plane(self.key_cache, self.k_scales, self.k_zeros if asym else None,
+                            L.KV_INT4_ASYM if asym else L.KV_INT4_SYM)
+        if self.v_mode == "int8":
+            vp = ops._plane(self.value_cache, self.v_scales, None, L.KV_INT8_G32)
+        else:
+            asym = self.v_mode == "int4_asym"
+            vp = ops._plane(self.value_cache, self.v_scales, self.v_zeros if asym else None,
+                            L.KV_INT4_ASYM if asym else L.KV_INT4_SYM)
+        return kp, vp
+
+    def caches(self):
+        return (self.key_cache, self.value_cache, self.k_scales, self.v_scales, self.k_zeros,
+                self.v_zeros)
+
     def decode(self, **kw) -> torch.Tensor:
         if self.k_mode == "int8" and self.v_mode == "int8":
             return ops.kint8_vint8_decode(
