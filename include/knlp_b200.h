@@ -219,6 +219,46 @@ int knlp_b200_decode_attention(const void* query, int q_dtype, const int64_t q_s
                                unsigned flags, void* stream);
 
 /*
+ * One decode step in ONE launch: append the step's new token of every sequence to the
+ * packed cache AND attend over the cache including it.  Replaces the two launches of a
+ * decode step of the reference, the cache write and the decode kernel
+ * (FusedInt4AttentionImpl: do_kv_cache_update :2483-2546 / forward :2600-2689, then
+ * _fused_decode :2851-2928); the idea is the reference's own, docs/fused-quant/latency.md:41.
+ * Arguments as knlp_b200_decode_attention, plus
+ *   new_tokens   key, value [n_seqs, n_kv_heads, head_dim] of dtype; strides {sequence,
+ *                head} in elements, innermost dimension contiguous; clip_ratio as in
+ *                knlp_b200_quant_append
+ *   seq_lens     the lengths BEFORE the append.  Sequence s gets its token at position
+ *                seq_lens[s] (block_table must already hold that position's block) and is
+ *                attended to over seq_lens[s] + 1 tokens; the caller adds 1 to its lengths
+ *                afterwards.  A sequence of length 0 attends to its new token alone.
+ * The token is quantized with the arithmetic of knlp_b200_quant_append (the same device
+ * function), so the stored bytes, scales and zeros are bit-identical to it; it takes part
+ * in the attention as the dequantized values a later step reads back.  Only layouts the
+ * balanced tensor-core kernel takes are supported: others return KNLP_ERR_STRIDE and
+ * nothing is launched (use knlp_b200_quant_append + knlp_b200_decode_attention there).
+ */
+typedef struct {
+  const void* key;
+  const void* value;
+  int64_t key_stride[2];
+  int64_t value_stride[2];
+  int32_t dtype; /* knlp_dtype */
+  float clip_ratio;
+} knlp_new_tokens;
+int knlp_b200_decode_append_attention(const void* query, int q_dtype, const int64_t q_stride[2],
+                                      const knlp_kv_plane* k_plane, const knlp_kv_plane* v_plane,
+                                      const int32_t* block_table, int64_t bt_stride,
+                                      const int32_t* seq_lens, int64_t num_blocks,
+                                      int n_seqs, int n_q_heads, int n_kv_heads, int head_dim,
+                                      int block_size, int max_seq_len,
+                                      float* workspace, int64_t workspace_floats,
+                                      int32_t* counters, int64_t counter_ints,
+                                      void* out, int out_dtype, int64_t out_row_stride,
+                                      unsigned flags, const knlp_new_tokens* new_tokens,
+                                      void* stream);
+
+/*
  * Merge n_parts partials per (sequence, q head) row.  No counterpart function
  * in the reference: the algebra is its in-loop online-softmax recurrence
  * (:808-815, :883-887) applied across splits.

@@ -33,6 +33,7 @@ SYMBOLS = (
     "knlp_b200_decode_splitk",
     "knlp_b200_decode_attention",
     "knlp_b200_decode_workspace",
+    "knlp_b200_decode_append_attention",
     "knlp_b200_combine",
     "knlp_b200_decode_noalloc",
     "knlp_b200_plugin_quantize",
@@ -52,6 +53,19 @@ class KvPlane(C.Structure):
         ("zeros_stride", C.c_int64 * 3),
         ("mode", C.c_int32),
         ("reserved", C.c_int32),
+    ]
+
+
+class NewTokens(C.Structure):
+    """knlp_new_tokens"""
+
+    _fields_ = [
+        ("key", C.c_void_p),
+        ("value", C.c_void_p),
+        ("key_stride", C.c_int64 * 2),
+        ("value_stride", C.c_int64 * 2),
+        ("dtype", C.c_int32),
+        ("clip_ratio", C.c_float),
     ]
 
 
@@ -98,6 +112,12 @@ def load() -> C.CDLL:
         C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
         C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int, C.c_int64,
         C.c_uint, C.c_void_p]
+    lib.knlp_b200_decode_append_attention.restype = C.c_int
+    lib.knlp_b200_decode_append_attention.argtypes = [
+        C.c_void_p, C.c_int, I64P, PL, PL, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
+        C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+        C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int, C.c_int64,
+        C.c_uint, C.POINTER(NewTokens), C.c_void_p]
     lib.knlp_b200_decode_workspace.restype = C.c_int
     lib.knlp_b200_decode_workspace.argtypes = [
         C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,

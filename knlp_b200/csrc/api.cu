@@ -247,15 +247,22 @@ int knlp_b200_decode_workspace(int n_seqs, int n_q_heads, int n_kv_heads, int he
   return KNLP_OK;
 }
 
-int knlp_b200_decode_attention(const void* query, int q_dtype, const int64_t q_stride[2],
+int knlp_b200_decode_append_attention(const void* query, int q_dtype, const int64_t q_stride[2],
                                const knlp_kv_plane* k_plane, const knlp_kv_plane* v_plane,
                                const int32_t* block_table, int64_t bt_stride,
                                const int32_t* seq_lens, int64_t num_blocks, int n_seqs,
                                int n_q_heads, int n_kv_heads, int head_dim, int block_size,
                                int max_seq_len, float* workspace, int64_t workspace_floats,
                                int32_t* counters, int64_t counter_ints, void* out, int out_dtype,
-                               int64_t out_row_stride, unsigned flags, void* stream) {
+                               int64_t out_row_stride, unsigned flags,
+                               const knlp_new_tokens* new_tokens, void* stream) {
   if (!out || !workspace || !counters) return KNLP_ERR_NULL;
+  if (new_tokens) {
+    if (!new_tokens->key || !new_tokens->value) return KNLP_ERR_NULL;
+    if (!dtype_ok(new_tokens->dtype)) return KNLP_ERR_DTYPE;
+    if (flags & (KNLP_DECODE_FORCE_GENERIC | KNLP_DECODE_USE_TMA | KNLP_DECODE_FIXED_SPLITS))
+      return KNLP_ERR_MODE;  // only the balanced kernel appends
+  }
   if (!dtype_ok(out_dtype)) return KNLP_ERR_DTYPE;
   const bool emit = (flags & KNLP_DECODE_EMIT_PARTIAL) != 0;
   if (emit && out_dtype != KNLP_F32) return KNLP_ERR_DTYPE;
@@ -277,9 +284,11 @@ int knlp_b200_decode_attention(const void* query, int q_dtype, const int64_t q_s
   }
   if (!(flags & (KNLP_DECODE_FORCE_GENERIC | KNLP_DECODE_USE_TMA | KNLP_DECODE_FIXED_SPLITS))) {
     rc = launch_decode_dq(a, workspace, workspace_floats, counters, counter_ints, max_seq_len, emit,
-                          sm_count(), st);
+                          sm_count(), new_tokens, st);
     if (rc <= 0) return rc;  // launched, or failed for good
   }
+  // a layout only the other kernels can address: they do not append
+  if (new_tokens) return KNLP_ERR_STRIDE;
   // fixed splits: split-context kernel into the workspace, then the combine kernel
   int n_splits = 1;
   int64_t need = 0;
@@ -302,6 +311,21 @@ int knlp_b200_decode_attention(const void* query, int q_dtype, const int64_t q_s
                         out_row_stride, emit ? fo + head_dim : nullptr,
                         emit ? fo + head_dim + 1 : nullptr, out_row_stride,
                         static_cast<int>(rows), head_dim, st);
+}
+
+int knlp_b200_decode_attention(const void* query, int q_dtype, const int64_t q_stride[2],
+                               const knlp_kv_plane* k_plane, const knlp_kv_plane* v_plane,
+                               const int32_t* block_table, int64_t bt_stride,
+                               const int32_t* seq_lens, int64_t num_blocks, int n_seqs,
+                               int n_q_heads, int n_kv_heads, int head_dim, int block_size,
+                               int max_seq_len, float* workspace, int64_t workspace_floats,
+                               int32_t* counters, int64_t counter_ints, void* out, int out_dtype,
+                               int64_t out_row_stride, unsigned flags, void* stream) {
+  return knlp_b200_decode_append_attention(
+      query, q_dtype, q_stride, k_plane, v_plane, block_table, bt_stride, seq_lens, num_blocks,
+      n_seqs, n_q_heads, n_kv_heads, head_dim, block_size, max_seq_len, workspace,
+      workspace_floats, counters, counter_ints, out, out_dtype, out_row_stride, flags, nullptr,
+      stream);
 }
 
 int knlp_b200_combine(const float* part_m, const float* part_l, const float* part_o,

@@ -60,7 +60,8 @@ void dq_workspace_size(int n_seqs, int n_q_heads, int n_kv_heads, int head_dim, 
 }
 
 int launch_decode_dq(const DecodeArgs& a, float* ws, int64_t ws_floats, int* ints, int64_t n_ints,
-                     int max_seq_len, bool emit_partial, int n_sms, cudaStream_t st) {
+                     int max_seq_len, bool emit_partial, int n_sms,
+                     const knlp_new_tokens* nt, cudaStream_t st) {
   DqParams dp{};
   if (decode_mma_layout(a, &dp.hpb_log2, &dp.page_log2)) return 1;
   // q rows are fetched with 16-byte loads
@@ -100,6 +101,16 @@ int launch_decode_dq(const DecodeArgs& a, float* ws, int64_t ws_floats, int* int
   // members (one long sequence on the whole machine) is merged by a second, parallel launch.
   dp.fuse = g <= 32 * n_pairs ? 1 : 0;
   dp.emit_partial = emit_partial ? 1 : 0;
+  if (nt) {
+    dp.new_key = nt->key;
+    dp.new_value = nt->value;
+    for (int i = 0; i < 2; ++i) {
+      dp.nk_stride[i] = nt->key_stride[i];
+      dp.nv_stride[i] = nt->value_stride[i];
+    }
+    dp.new_dtype = nt->dtype;
+    dp.clip_ratio = nt->clip_ratio;
+  }
   const bool split = n_rep <= 4;
   const int rc = with_pair(a.k.mode, a.v.mode, [&](auto k, auto v) {
     return launch_dq_pair<decltype(k)::value, decltype(v)::value>(a, dp, split, st);

@@ -31,6 +31,7 @@
 #include <atomic>
 
 #include "decode_mma_common.cuh"
+#include "quant_row.cuh"
 
 namespace knlp {
 
@@ -47,6 +48,14 @@ struct DqParams {
   int* pair_info;  // [2 * n_pairs]: first slot and number of parts (for the combine kernel)
   int fuse;        // 1: the last member of a pair merges its parts into a.out
   int emit_partial;  // fused merge writes fp32 rows [o (un-normalised), m, l] instead
+  // The step's new token, appended inside the launch (new_key == nullptr: none):
+  // [n_seqs, n_kv_heads, head_dim] of new_dtype, strides {sequence, head} in elements.
+  // It is quantized into the cache at position seq_lens[s] and attended to as well.
+  const void* new_key;
+  const void* new_value;
+  int64_t nk_stride[2], nv_stride[2];
+  int new_dtype;
+  float clip_ratio;
 };
 
 namespace {
@@ -231,6 +240,73 @@ __device__ __noinline__ void merge_pair(const float* pm, const float* pl, const 
   }
 }
 
+// The step's new token of one (sequence, kv head), done by ONE warp of the pair's last
+// member: quantize K and V with the write path's own arithmetic (quant_row.cuh), store
+// them at the token's slot, and leave what the attention needs of it in shared memory -
+// the scaled scores of the head's q rows against the DEQUANTIZED key (as later steps will
+// read it) and the dequantized value row - so that the token joins this CTA's partial as
+// one more tile, without a round trip through global memory.
+template <int HD, int KMODE, int VMODE>
+__device__ __noinline__ void append_token(const void* ksrc, const void* vsrc, const int src_dt,
+                                          uint8_t* k_crow, __half* k_srow, __half* k_zrow,
+                                          uint8_t* v_crow, __half* v_srow, __half* v_zrow,
+                                          const void* q, const int q_dt, const int64_t q_row0,
+                                          const int64_t q_head_stride, const int n_rep,
+                                          const float clip_ratio, float* s_new, float* v_new) {
+  const int lane = threadIdx.x & 31;
+  const int e0 = lane * 4;
+  const bool active = e0 < HD;
+  const bool leader = active && ((lane & 7) == 0);
+  float x[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  int c[4];
+  float sc, mn;
+  // ---- key
+  if (active) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) x[i] = load_elem_rt(ksrc, e0 + i, src_dt);
+  }
+  quantize4(KMODE, x, lane, clip_ratio, c, sc, mn);
+  if (active) store_quantized4(KMODE, c, sc, mn, k_crow, k_srow, k_zrow, e0, leader, true);
+  {
+    const float s16 = __half2float(__float2half_rn(sc));
+    const float z16 = KMODE == KNLP_KV_INT4_ASYM ? __half2float(__float2half_rn(mn)) : 0.0f;
+    float kh[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float code = static_cast<float>(KMODE == KNLP_KV_INT4_SYM ? c[i] - 8 : c[i]);
+      kh[i] = active ? code * s16 + z16 : 0.0f;
+    }
+    const float mul = rsqrtf(static_cast<float>(HD)) * 1.4426950408889634f;  // log2 domain
+    for (int hs = 0; hs < n_rep; ++hs) {
+      float dot = 0.0f;
+      if (active) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          dot = fmaf(load_elem_rt(q, q_row0 + hs * q_head_stride + e0 + i, q_dt), kh[i], dot);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      if (lane == 0) s_new[hs] = dot * mul;
+    }
+  }
+  // ---- value
+  if (active) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) x[i] = load_elem_rt(vsrc, e0 + i, src_dt);
+  }
+  quantize4(VMODE, x, lane, clip_ratio, c, sc, mn);
+  if (active) {
+    store_quantized4(VMODE, c, sc, mn, v_crow, v_srow, v_zrow, e0, leader, true);
+    const float s16 = __half2float(__float2half_rn(sc));
+    const float z16 = VMODE == KNLP_KV_INT4_ASYM ? __half2float(__float2half_rn(mn)) : 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float code = static_cast<float>(VMODE == KNLP_KV_INT4_SYM ? c[i] - 8 : c[i]);
+      v_new[e0 + i] = code * s16 + z16;
+    }
+  }
+}
+
 template <int HD, int KMODE, int VMODE, bool SPLIT, int HPBL>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
@@ -275,15 +351,18 @@ decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
   const int Lid = static_cast<int>(blockIdx.x % dp.n_cols) * dp.n_ranks +
                   static_cast<int>(blockIdx.x / dp.n_cols);
 
+  // a sequence without cached tokens still has work when the step appends one to it
+  const bool appending = dp.new_key != nullptr;
   auto seq_chunks = [&](int s) -> int {
     const int L = __ldg(a.seq_lens + s);
-    return L > 0 ? (L + CT - 1) / CT : 0;
+    if (L < 0 || (L == 0 && !appending)) return 0;
+    return L > CT ? (L + CT - 1) / CT : 1;
   };
 
   // ---------------- sequences without tokens: their output rows are zero ----------------
   if (dp.fuse) {
     for (int s = Lid; s < S; s += Gn) {
-      if (__ldg(a.seq_lens + s) > 0) continue;
+      if (seq_chunks(s) > 0) continue;
       const int row_elems = dp.emit_partial ? HD + 2 : HD;
       for (int i = tid; i < a.n_q_heads * row_elems; i += kThreads) {
         const int r = i / row_elems, e = i % row_elems;
@@ -297,7 +376,7 @@ decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
     }
   } else {
     for (int p = Lid * kThreads + tid; p < n_pairs; p += Gn * kThreads) {
-      if (__ldg(a.seq_lens + p / HBn) <= 0) {
+      if (seq_chunks(p / HBn) == 0) {
         dp.pair_info[2 * p] = 0;
         dp.pair_info[2 * p + 1] = 0;
       }
@@ -457,8 +536,10 @@ decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
       s_park[5] = last_pair ? 1 : 0;
     }
 
+    // the pair's last member also appends the step's new token
+    const bool has_new = appending && slot - first_slot == parts - 1;
     bool have_work = true;
-    if (!home) {  // one thread looks, so that the whole CTA goes the same way
+    if (!home && !has_new) {  // one thread looks, so that the whole CTA goes the same way
       if (tid == 0) s_flag = dyn0 + *reinterpret_cast<volatile int*>(ticket) < n_chunks ? 1 : 0;
       __syncthreads();
       have_work = s_flag != 0;
@@ -1086,6 +1167,32 @@ decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
         }
       }
     }
+    // the step's new token (the pair's last member only): one warp per kv head of the pair
+    float* sm_snew = sm_l + kWarpsCta * kHeadSlots;  // [HPB][8] scaled scores, log2 domain
+    float* sm_vnew = sm_snew + HPB * 8;              // [HPB][HD] dequantized value rows
+    const bool new_here = appending && s_park[0] - s_park[1] == s_park[2] - 1;
+    if (new_here && w_tile == 0) {
+      const int seq_e = s_park[3], kvh_e = s_park[4] * HPB + w_head;
+      const int len_e = __ldg(a.seq_lens + seq_e);
+      int blk = __ldg(a.block_table + static_cast<int64_t>(seq_e) * a.bt_stride +
+                      (len_e >> dp.page_log2));
+      blk = blk < 0 ? 0 : (blk > max_blk ? max_blk : blk);
+      const int off = len_e & page_mask;
+      auto row = [&](const Plane& pl, auto* base, const int64_t* st) {
+        return base + (static_cast<int64_t>(blk) * st[0] + static_cast<int64_t>(off) * st[1] +
+                       static_cast<int64_t>(kvh_e) * st[2]);
+      };
+      append_token<HD, KMODE, VMODE>(
+          static_cast<const uint8_t*>(dp.new_key) +
+              (seq_e * dp.nk_stride[0] + kvh_e * dp.nk_stride[1]) * (dp.new_dtype == KNLP_F32 ? 4 : 2),
+          static_cast<const uint8_t*>(dp.new_value) +
+              (seq_e * dp.nv_stride[0] + kvh_e * dp.nv_stride[1]) * (dp.new_dtype == KNLP_F32 ? 4 : 2),
+          dp.new_dtype, row(a.k, a.k.codes, a.k.cs), row(a.k, a.k.scales, a.k.ss),
+          kAsymK ? row(a.k, a.k.zeros, a.k.zs) : nullptr, row(a.v, a.v.codes, a.v.cs),
+          row(a.v, a.v.scales, a.v.ss), kAsymV ? row(a.v, a.v.zeros, a.v.zs) : nullptr, a.q,
+          a.q_dtype, static_cast<int64_t>(seq_e) * a.q_stride[0] + kvh_e * n_rep * a.q_stride[1],
+          a.q_stride[1], n_rep, dp.clip_ratio, sm_snew + w_head * 8, sm_vnew + w_head * HD);
+    }
     __syncthreads();
     // this CTA's partial of the pair: rows (kv head hl, q head hs), merged over the tiles
     {
@@ -1103,8 +1210,15 @@ decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
           const int w = hl + (t << hpb_log2);
           if (sm_l[w * kHeadSlots + hs] > 0.0f) mm = fmaxf(mm, sm_m[w * kHeadSlots + hs]);
         }
+        if (new_here) mm = fmaxf(mm, sm_snew[hl * 8 + hs]);
         float ll = 0.0f;
         float4 oo = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (new_here) {  // the appended token: one more tile of one token, p = 2^(s - m)
+          const float wgt = fast_exp2(sm_snew[hl * 8 + hs] - mm);
+          const float4 v = *reinterpret_cast<const float4*>(sm_vnew + hl * HD + 4 * e4);
+          ll = wgt;
+          oo = make_float4(v.x * wgt, v.y * wgt, v.z * wgt, v.w * wgt);
+        }
 #pragma unroll
         for (int t = 0; t < tiles; ++t) {
           const int w = hl + (t << hpb_log2);

@@ -408,11 +408,18 @@ def decode_attention(
     block_table: torch.Tensor, seq_lens: torch.Tensor, num_kv_heads: int, head_size: int,
     block_size: int, *, out_dtype=None, max_seq_len: Optional[int] = None,
     emit_partial: bool = False, out: Optional[torch.Tensor] = None, flags: int = 0,
+    new_key: Optional[torch.Tensor] = None, new_value: Optional[torch.Tensor] = None,
+    clip_ratio: Optional[float] = None,
 ) -> torch.Tensor:
     """Decode attention balanced inside one launch (``knlp_b200_decode_attention``).
     Returns [S, Hq, d] in ``out_dtype`` (default: the query's); with ``emit_partial`` the
     merged softmax partial per row instead, fp32 [S, Hq, d + 2] = [o un-normalised, m, l]
-    (what a rank of a context shard all-gathers)."""
+    (what a rank of a context shard all-gathers).
+
+    With ``new_key`` / ``new_value`` ([S, Hkv, d]) the same launch first appends the
+    step's new token of every sequence to the cache at position ``seq_lens[s]`` (the
+    lengths BEFORE the append) and attends over ``seq_lens[s] + 1`` tokens
+    (``knlp_b200_decode_append_attention``)."""
     dev = _need_cuda(query, block_table, seq_lens)
     if block_table.dtype != torch.int32 or seq_lens.dtype != torch.int32:
         raise TypeError("block_table and seq_lens must be int32")
@@ -434,14 +441,29 @@ def decode_attention(
                           device=dev)
     if not out.is_contiguous():
         raise ValueError("out must be contiguous")
+    nt = None
+    if new_key is not None or new_value is not None:
+        if new_key is None or new_value is None:
+            raise ValueError("the fused append needs both new_key and new_value")
+        _need_cuda(new_key, new_value)
+        if new_key.dtype != new_value.dtype or new_key.shape != (S, num_kv_heads, d) or (
+                new_value.shape != new_key.shape):
+            raise ValueError("new_key / new_value must be [S, num_kv_heads, head_size] of one dtype")
+        nt = _lib.NewTokens()
+        nt.key, nt.value = new_key.data_ptr(), new_value.data_ptr()
+        nt.key_stride, nt.value_stride = _stride2(new_key), _stride2(new_value)
+        nt.dtype = _dt(new_key)
+        nt.clip_ratio = float(OUTLIER_CLIP_RATIO if clip_ratio is None else clip_ratio)
     with torch.cuda.device(dev):
-        rc = _lib.load().knlp_b200_decode_attention(
+        rc = _lib.load().knlp_b200_decode_append_attention(
             query.data_ptr(), _dt(query), _stride2(query), C.byref(k_plane), C.byref(v_plane),
             block_table.data_ptr(), block_table.stride(0), seq_lens.data_ptr(), num_blocks,
             S, Hq, num_kv_heads, head_size, block_size, max_seq_len,
             ws.data_ptr(), ws.numel(), counters.data_ptr(), counters.numel(),
-            out.data_ptr(), _DT[out.dtype], out.shape[-1], flags, _stream(dev))
-    _lib.check(rc, "knlp_b200_decode_attention")
+            out.data_ptr(), _DT[out.dtype], out.shape[-1], flags,
+            C.byref(nt) if nt is not None else None, _stream(dev))
+    _lib.check(rc, "knlp_b200_decode_append_attention" if nt is not None
+               else "knlp_b200_decode_attention")
     return out
 
 

@@ -31,7 +31,7 @@ def _zeros_equal(a, b):
     return bool(np.all((a == b) | (((a | b) & 0x7FFF) == 0)))
 
 
-@pytest.mark.parametrize("mode", ["k8v4", "int4", "k8v4_two_calls"])
+@pytest.mark.parametrize("mode", ["k8v4", "int4", "k8v4_two_calls", "k8v4_fused", "int4_fused"])
 def test_append_then_attend_64_steps(mode, cuda_device):
     from knlp_b200 import ops
     dev = cuda_device
@@ -40,9 +40,10 @@ def test_append_then_attend_64_steps(mode, cuda_device):
     # lengths that put the appended token on every position of a page over the 64 steps,
     # first and last slot of a page included, and that move the end of the sequence through
     # the balanced kernel's chunk (64 tokens) and the fixed splits' boundaries
-    lens0 = [15, 16, 31, 100, 257, 1000, 1, 2047]
+    lens0 = [15, 16, 31, 100, 257, 1000, 1, 2047, 0]
     S = len(lens0)
     k8 = mode.startswith("k8v4")
+    fused = mode.endswith("_fused")  # the step's token is appended by the decode launch itself
     pages = [(L + n_steps + P - 1) // P for L in lens0]
     nb = sum(pages) + 3
     perm = rng.permutation(nb)
@@ -84,6 +85,8 @@ def test_append_then_attend_64_steps(mode, cuda_device):
 
     # prefill
     for s, n in enumerate(lens0):
+        if n == 0:
+            continue
         k_b = bf16(rng.standard_normal((n, Hkv, d)).astype(np.float32) * chs)
         v_b = bf16(rng.standard_normal((n, Hkv, d)).astype(np.float32) * chs)
         pos = np.arange(n)
@@ -95,12 +98,27 @@ def test_append_then_attend_64_steps(mode, cuda_device):
         k_b = bf16(rng.standard_normal((S, Hkv, d)).astype(np.float32) * chs)
         v_b = bf16(rng.standard_normal((S, Hkv, d)).astype(np.float32) * chs)
         slots = bt[np.arange(S), lens // P].astype(np.int64) * P + lens % P
-        append(k_b, v_b, slots)
-        lens = lens + 1
-        lens_d = torch.from_numpy(lens).to(dev)
-        # every step runs on the GPU (the loop is the point); the oracle checks some
-        out = ops.decode_attention(q.to(dev), kp, vp, nb, bt_d, lens_d, Hkv, d, P,
-                                   out_dtype=torch.float32, max_seq_len=int(lens.max()))
+        if fused:
+            # oracle: write, then attend; GPU: ONE launch given the lengths before the append
+            kf, vf = k_b.float().numpy(), v_b.float().numpy()
+            if k8:
+                O.reshape_and_cache_k_int8(kf, kc, ks, slots)
+                O.reshape_and_cache_v_only_int4(vf, vc, vs, slots, vz, asymmetric=True)
+            else:
+                O.reshape_and_cache_int4(kf, vf, kc, vc, ks, vs, slots, kz, vz, asymmetric=True)
+            out = ops.decode_attention(q.to(dev), kp, vp, nb, bt_d, torch.from_numpy(lens).to(dev),
+                                       Hkv, d, P, out_dtype=torch.float32,
+                                       max_seq_len=int(lens.max()) + 1,
+                                       new_key=k_b.to(dev), new_value=v_b.to(dev))
+            lens = lens + 1
+            lens_d = torch.from_numpy(lens).to(dev)
+        else:
+            append(k_b, v_b, slots)
+            lens = lens + 1
+            lens_d = torch.from_numpy(lens).to(dev)
+            # every step runs on the GPU (the loop is the point); the oracle checks some
+            out = ops.decode_attention(q.to(dev), kp, vp, nb, bt_d, lens_d, Hkv, d, P,
+                                       out_dtype=torch.float32, max_seq_len=int(lens.max()))
         if step in CHECK_STEPS:
             qf = q.float().numpy()
             if k8:
