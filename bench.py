@@ -333,7 +333,7 @@ def summarize(name, w, res, K, peak_gbs):
 
 
 def measure_append_loop(torch, ops, workloads, name, dev, K, W, barrier, peak_gbs, n_sub=64,
-                        head_slice=None):
+                        head_slice=None, fused=False):
     """Config 5 as stated: every step appends one new bf16 token per sequence to the cache
     (quantize-append, one launch for both planes) and then attends over the full cache, for
     ``n_sub`` consecutive steps with growing lengths.  The slots and lengths of all steps are
@@ -351,6 +351,7 @@ def measure_append_loop(torch, ops, workloads, name, dev, K, W, barrier, peak_gb
         slots.append(bt[torch.arange(S), pos // PAGE] * PAGE + pos % PAGE)
         lens.append((pos + 1).to(torch.int32))
     lens_d = torch.stack(lens).to(dev)
+    lens0_d = lens_d - 1
     slots_d = torch.stack(slots).to(dev)
     g = torch.Generator(device=dev).manual_seed(99)
     knew = torch.randn(n_sub, S, w.n_kv_heads, d, device=dev, generator=g).to(torch.bfloat16)
@@ -360,9 +361,14 @@ def measure_append_loop(torch, ops, workloads, name, dev, K, W, barrier, peak_gb
 
     def loop():
         for i in range(n_sub):
-            ops.quant_append(knew[i], vnew[i], kp, vp, slots_d[i], PAGE)
-            ops.decode_attention(w.query, kp, vp, nblocks, w.block_table, lens_d[i], w.n_kv_heads,
-                                 d, PAGE, max_seq_len=max_len, out=out)
+            if fused:  # ONE launch appends the token and attends (lengths before the append)
+                ops.decode_attention(w.query, kp, vp, nblocks, w.block_table, lens0_d[i],
+                                     w.n_kv_heads, d, PAGE, max_seq_len=max_len, out=out,
+                                     new_key=knew[i], new_value=vnew[i])
+            else:
+                ops.quant_append(knew[i], vnew[i], kp, vp, slots_d[i], PAGE)
+                ops.decode_attention(w.query, kp, vp, nblocks, w.block_table, lens_d[i],
+                                     w.n_kv_heads, d, PAGE, max_seq_len=max_len, out=out)
 
     replay, mode = capture(torch, loop, warm=1)
     for _ in range(max(1, W // 4)):
@@ -377,13 +383,15 @@ def measure_append_loop(torch, ops, workloads, name, dev, K, W, barrier, peak_gb
     alg = sum((toks + S * (i + 1)) * per_tok + qo + S * w.n_kv_heads * (2 * d * 2) + S * per_tok
               for i in range(n_sub)) / n_sub
     ms = total_ms / reps / n_sub
-    return {"workload": name + f" x {n_sub} append+attend steps", "us_per_step": ms * 1e3,
+    return {"workload": name + f" x {n_sub} append+attend steps, " +
+                        ("append fused into the decode launch" if fused else "append launch + decode launch"),
+            "us_per_step": ms * 1e3,
             "us_median": pct(each, 0.5) / n_sub * 1e3, "us_p10": pct(each, 0.1) / n_sub * 1e3,
             "us_p90": pct(each, 0.9) / n_sub * 1e3, "algorithmic_bytes": alg,
             "tb_per_s": alg / (ms / 1e3) / 1e12, "frac": alg / (ms / 1e3) / 1e9 / peak_gbs,
             "steps": reps * n_sub, "l2": "working set larger than L2", "mode": mode,
             "n_seqs": S, "kv_heads_per_gpu": w.n_kv_heads, "kv": f"K {w.k_mode} / V {w.v_mode}",
-            "launches_per_step": 2}
+            "launches_per_step": 1 if fused else 2}
 
 
 def run_ours(args):
@@ -569,11 +577,12 @@ def run_ours(args):
             secondary.append(row)
             del w2, r2, _
             torch.cuda.empty_cache()
-        row = measure_append_loop(torch, ops, workloads, "mixed_k8v4", dev, Ks, Ws, barrier,
-                                  peak_gbs, head_slice=head_slice_for(8))
-        row["parallelism"] = "single GPU" if world == 1 else f"kv-head shard x{world}"
-        secondary.append(row)
-        torch.cuda.empty_cache()
+        for fused in (False, True):
+            row = measure_append_loop(torch, ops, workloads, "mixed_k8v4", dev, Ks, Ws, barrier,
+                                      peak_gbs, head_slice=head_slice_for(8), fused=fused)
+            row["parallelism"] = "single GPU" if world == 1 else f"kv-head shard x{world}"
+            secondary.append(row)
+            torch.cuda.empty_cache()
         if world > 1:
             # config 3 as stated: one long sequence split into contiguous context segments
             w3 = workloads.config("llama8b_b1_384k", dev, ctx_shard=(world, rank))

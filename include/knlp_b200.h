@@ -291,8 +291,8 @@ int knlp_b200_combine(const float* part_m, const float* part_l, const float* par
  * Arithmetic is carried out in x's dtype as the reference does (amax floor 1e-8, scale
  * and quotient each rounded to that dtype), integer rounding is half-to-even, so codes
  * and scales are bit-identical to the reference's.  A row that is all zero in fp16
- * (where the floor rounds to 0) is 0 / 0 in the reference; here its codes are the range
- * minimum and its scale 0.
+ * (where the floor rounds to 0) is 0 / 0 in the reference, whose NaN converts to code 0;
+ * here too its codes are 0 and its scale 0.
  */
 int knlp_b200_plugin_quantize(const void* x, int dtype, int64_t n_rows, int dim, int group,
                               int bits, int8_t* q, void* scale, void* stream);

@@ -63,7 +63,9 @@ plugin_quantize_kernel(const void* __restrict__ x, int8_t* __restrict__ q,
   }
   for (int i = lo + lane; i < hi; i += 32) {
     const float y = round_to_dtype<DT>(__fdiv_rn(load_elem<DT>(x, base + i), sc));
-    const float r = fminf(fmaxf(rintf(y), qmin), qmax);  // NaN (0 / 0 in fp16) clamps to qmin
+    // 0 / 0 (an all-zero row in fp16, where the 1e-8 floor rounds to 0) is NaN: code 0, which
+    // is what the reference's NaN -> int8 conversion yields
+    const float r = y != y ? 0.0f : fminf(fmaxf(rintf(y), qmin), qmax);
     q[base + i] = static_cast<int8_t>(static_cast<int>(r));
   }
 }

@@ -272,8 +272,52 @@ def gen_kfp16_cases(m, out):
     out["kfp16_modes"] = rec
 
 
+def gen_contig_cases(out):
+    """The contiguous head-major symmetric cache of the reference's kernel benches:
+    quantize_and_pack_int4, dequant_int4 and pipeline_A of scripts/v29_flash_bench.py
+    (:40-97), run on CPU tensors (the module imports without a GPU; its shape constants are
+    14 query / 2 kv heads, head_dim 64)."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location(
+        "v29_flash_bench", os.path.join(REF, "scripts", "v29_flash_bench.py"))
+    m = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(m)
+    g = torch.Generator().manual_seed(29)
+    B, T, hd = 2, 96, m.HEAD_DIM
+    k = torch.randn(B, m.N_KV_HEADS, T, hd, generator=g).to(torch.float16)
+    v = (torch.randn(B, m.N_KV_HEADS, T, hd, generator=g) * 0.7 + 0.1).to(torch.float16)
+    k[..., 5] *= 10  # an outlier channel
+    k[0, 0, 3] = 0   # an all-zero row
+    v[1, 1, 7] = torch.arange(hd, dtype=torch.float16) * 0.5  # exact ties after scaling
+    q = torch.randn(B, m.N_HEADS, 1, hd, generator=g).to(torch.float16)
+    kp, ks = m.quantize_and_pack_int4(k)
+    vp, vs = m.quantize_and_pack_int4(v)
+    # pipeline_A's arithmetic (dequantize, repeat the kv heads, SDPA) carried out in fp32:
+    # the packed tensors and the dequantized values are the contract, the fp16 rounding of
+    # its SDPA is not
+    kd, vd = m.dequant_int4(kp, ks), m.dequant_int4(vp, vs)
+    n_rep = m.N_HEADS // m.N_KV_HEADS
+    o = torch.nn.functional.scaled_dot_product_attention(
+        q.float(), kd.float().repeat_interleave(n_rep, dim=1),
+        vd.float().repeat_interleave(n_rep, dim=1), is_causal=False)
+    out["contig_sym"] = dict(
+        key=k.float().numpy(), value=v.float().numpy(), query=q.float().numpy(),
+        k_packed=kp.numpy(), v_packed=vp.numpy(),
+        k_scales=ks.view(torch.int16).numpy().view(np.uint16),
+        v_scales=vs.view(torch.int16).numpy().view(np.uint16),
+        k_dequant=kd.float().numpy(), v_dequant=vd.float().numpy(), out=o.numpy(),
+        n_heads=np.int32(m.N_HEADS), n_kv_heads=np.int32(m.N_KV_HEADS))
+    print("contiguous symmetric case done", flush=True)
+
+
 def main():
     out = {}
+    if "--only-contig" in sys.argv:
+        gen_contig_cases(out)
+        for name, rec in out.items():
+            np.savez_compressed(os.path.join(HERE, name + ".npz"), **rec)
+            print("saved", name)
+        return
     if "--only-kfp16" in sys.argv:
         gen_kfp16_cases(load_reference(), out)
         for name, rec in out.items():
