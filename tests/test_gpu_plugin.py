@@ -146,3 +146,71 @@ def test_quant_backend_calibrate_picks_bits(cuda_device):
     f.configure(128, mc, W_min=32)
     f.calibrate(model, tokens, 128, str(cuda_device), mc)
     assert f.layer_bits == [4, 4, 4] and f.compression_ratio() == 0.25
+
+
+@pytest.mark.parametrize("bits,hd", [(4, 32), (8, 32), (4, 64)])
+def test_packed_backend_run_decode_matches_oracle_cache(bits, hd, cuda_device):
+    """quant_packed: the far segment lives in a REAL packed cache read by the decode kernel
+    inside the model's attention.  Against the same decode over a float cache whose far
+    segment the kv oracle quantized (INT4 asymmetric / INT8, group 32) and dequantized on
+    the CPU: the logits must agree to the precision of the attention path."""
+    from transformers import GPT2Config, GPT2LMHeadModel
+    from transformers.cache_utils import DynamicCache
+    from knlp_b200 import backends as B
+    from oracle import kv_oracle as KO
+    n_head = 4
+    cfg = GPT2Config(n_layer=3, n_head=n_head, n_embd=n_head * hd, vocab_size=300, n_positions=512)
+    torch.manual_seed(11)
+    model = GPT2LMHeadModel(cfg).eval().to(cuda_device)
+    mc = dict(n_layers=3, n_kv_heads=n_head, head_dim=hd)
+    g = torch.Generator().manual_seed(5)
+    prefix = torch.randint(0, 300, (1, 120), generator=g).to(cuda_device)
+    cont = torch.randint(0, 300, (1, 6), generator=g).to(cuda_device)
+    W_min, W_sink, L = 32, 4, 120
+    far_end = L - W_min
+
+    b = B.get_backend("quant_packed")
+    b.configure(L, mc, W_min=W_min, W_sink=W_sink)
+    b.calibrated, b.layer_bits = True, [bits] * 3
+    logits, stats = b.run_decode(model, prefix, cont, str(cuda_device), 512)
+    assert logits.shape == (1, 7, 300) and len(stats) == 6
+    n_far = far_end - W_sink
+    assert stats[0].n_compressed == n_far and stats[0].n_full == W_min + W_sink + 1
+    # real bytes: per (token, kv head) 2 x (hd/2 + 4 hd/32) for INT4 asym, 2 x (hd + 2 hd/32) INT8
+    per_tok = n_head * (2 * (hd // 2 + 4 * hd // 32) if bits == 4 else 2 * (hd + 2 * hd // 32))
+    assert stats[0].kv_bytes_compressed == n_far * per_tok * 3
+    assert model.config._attn_implementation != "knlp_b200_packed"  # restored
+
+    with torch.no_grad():
+        out = model(prefix, use_cache=True)
+        past = out.past_key_values
+        ref_logits = [out.logits[:, -1:, :]]
+        cache = DynamicCache()
+        for li in range(3):
+            kv = []
+            for t in (past.layers[li].keys, past.layers[li].values):
+                far = t[0, :, W_sink:far_end, :].permute(1, 0, 2).float().cpu().numpy()  # [T, H, D]
+                if bits == 4:
+                    packed, sc, zp = KO.quant_int4_asym(far)
+                    hat = KO.dequant_int4(packed, sc, zp)
+                else:
+                    codes, sc = KO.quant_int8_group(far)
+                    hat = KO.dequant_int8(codes, sc)
+                hat = torch.from_numpy(np.ascontiguousarray(hat)).permute(1, 0, 2)[None]
+                hat = hat.to(t.dtype).to(cuda_device)
+                kv.append(torch.cat([t[:, :, :W_sink], hat, t[:, :, far_end:]], dim=2))
+            cache.update(kv[0], kv[1], li)
+        pos = L
+        for step in range(6):
+            out = model(cont[:, step:step + 1], past_key_values=cache, use_cache=True,
+                        position_ids=torch.tensor([[pos]], device=cuda_device))
+            cache = out.past_key_values
+            ref_logits.append(out.logits)
+            pos += 1
+    ref = torch.cat(ref_logits, dim=1)
+    assert torch.allclose(logits, ref, atol=2e-3, rtol=1e-3), (logits - ref).abs().max()
+
+    d = B.get_backend("dense")
+    d.configure(L, mc)
+    dl, _ = d.run_decode(model, prefix, cont, str(cuda_device), 512)
+    assert (dl - logits).abs().max() > 1e-4  # the quantization is really applied
