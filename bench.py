@@ -273,6 +273,9 @@ class Timed:
         return total, each
 
 
+GRAPHS = []  # every captured graph, so that teardown can release them all
+
+
 def capture(torch, fn, warm: int = 3):
     """fn() captured in a CUDA graph (after ``warm`` eager calls, which also size the library's
     workspace); falls back to the eager calls if capture is refused."""
@@ -287,6 +290,7 @@ def capture(torch, fn, warm: int = 3):
     except RuntimeError as exc:
         torch.cuda.synchronize()
         return fn, f"eager calls (graph capture failed: {str(exc)[:80]})"
+    GRAPHS.append(graph)
     return graph.replay, "captured in one CUDA graph, replayed"
 
 
@@ -459,8 +463,7 @@ def run_ours(args):
         # profiling run (under ncu): kernel timing only, no end-to-end, secondary or CPU legs
         if rank == 0:
             print(json.dumps({"profile_run": True, **head}), flush=True)
-        if world > 1:
-            dist.destroy_process_group()
+        teardown(torch, dist, world)
         return
 
     # ---------------- end to end through the operator API with host buffers
@@ -659,7 +662,23 @@ def run_ours(args):
                 "cpu": "PyTorch eager fp32 dequantize -> SDPA, whole workload",
                 "gpu_us_median": pct(r1["each_ms"], 0.5) * 1e3, "gpu": "decode_attention, " + r1["l2"]}
         print(json.dumps(line), flush=True)
+    teardown(torch, dist, world)
+
+
+def teardown(torch, dist, world):
+    """Release every captured CUDA graph before the process group goes: a graph that holds
+    a captured NCCL collective keeps the communicator busy and its destruction would wait
+    for ever."""
+    import gc
+    torch.cuda.synchronize()
+    for g in GRAPHS:
+        g.reset()
+    GRAPHS.clear()
+    gc.collect()
+    torch.cuda.synchronize()
     if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
         dist.destroy_process_group()
 
 
