@@ -324,6 +324,34 @@ def measure_decode(torch, ops, w, K: int, W: int, barrier, ctx_mode: bool, shard
                    else "inputs larger than L2 (no flush needed)")}, replay
 
 
+def ctx_breakdown(torch, ops, w, shardlib, barrier, n=30):
+    """Where a context-sharded step spends its time: CUDA events around the three pieces of
+    an EAGER step (decode launch that emits the rank's packed partial; NCCL all-gather;
+    merge of the ranks' partials), median over ``n`` steps, plus the whole eager step."""
+    dev = w.query.device
+    kp, vp = w.planes()
+    S, Hq, d = w.query.shape
+    packed = torch.empty((S, Hq, d + 2), dtype=torch.float32, device=dev)
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(n)]
+    for i in range(-3, n):
+        e = ev[max(i, 0)]
+        barrier()
+        e[0].record()
+        ops.decode_attention(w.query, kp, vp, w.key_cache.shape[0], w.block_table, w.seq_lens,
+                             w.n_kv_heads, d, PAGE, max_seq_len=w.max_seq_len, emit_partial=True,
+                             out=packed)
+        e[1].record()
+        gathered = shardlib.all_gather_packed(packed)
+        e[2].record()
+        ops.combine_packed(gathered, out_dtype=w.query.dtype)
+        e[3].record()
+    torch.cuda.synchronize()
+    med = lambda a, b: pct([e[a].elapsed_time(e[b]) * 1e3 for e in ev], 0.5)
+    return {"decode_emit_partial_us": med(0, 1), "all_gather_us": med(1, 2),
+            "merge_ranks_us": med(2, 3), "eager_step_us": med(0, 3),
+            "note": "eager calls, rank 0's events; launch gaps are inside the pieces"}
+
+
 def summarize(name, w, res, K, peak_gbs):
     ms = res["total_ms"] / K
     alg = w.algorithmic_bytes()
@@ -593,6 +621,7 @@ def run_ours(args):
             row = summarize("llama8b_b1_384k", w3, r3, Ks, peak_gbs)
             row["parallelism"] = f"context shard x{world} (+1 NCCL all-gather of partials)"
             row["mode"] = r3["mode"]
+            row["breakdown"] = ctx_breakdown(torch, ops, w3, shardlib, barrier)
             secondary.append(row)
             del w3, r3, _
             torch.cuda.empty_cache()

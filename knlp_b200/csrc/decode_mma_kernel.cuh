@@ -1,6 +1,60 @@
-// The split-context tensor-core decode kernel and its launch templates.  Included by the
-// host file (which only declares the instantiations) and by one small translation unit
-// per pair of K/V modes, so the instantiations compile in parallel.
+// Split-context GQA decode attention over the packed KV cache (sm_100a).
+//
+// The hot kernel of the library.  It replaces the reference's
+// _fused_int4_decode_kernel (fused-quant/fused_int4.v0.1.0.py:656-894) and
+// _kint8_vint4_decode_kernel (:1318-1493), which run one program per
+// (sequence, q head), stream the whole context through it and re-read K/V once
+// per q head of a group.  Here a CTA owns (sequence, block of kv heads,
+// context split); every K/V byte is read from HBM once and serves all q heads
+// of its group.
+//
+// Data movement: each stage of the pipeline is TT tokens x HPB kv heads of
+// codes, scales and zeros (HPB <= 4 heads, one warp per head and 16-token tile),
+// copied global -> shared with cp.async in 16-byte pieces dealt in memory order,
+// three or four stages deep.  Code rows are stored warp-major in shared memory
+// (the 16 rows a warp consumes are contiguous) with an xor swizzle of the 16-byte
+// column, scale rows xor-permuted by their place in the bank period, so that the
+// cp.async writes, the ldmatrix reads and the scale loads are bank-conflict free.
+// While whole stages lie ahead the loop body carries no end-of-sequence test.
+//
+// Math: the per-token work is far too much for CUDA-core FMAs at HBM speed
+// (2 * n_rep * head_dim FMAs per 160 bytes), so both products run on the tensor
+// cores as m16n8k16 f16 MMAs with the 16 TOKENS of a tile on the M side and the
+// q heads of the kv group on the N side, which keeps the tile dense for GQA:
+//   scores  S_g[token, col] = sum_{d in group g} code[token, d] * q[col, d]
+//   output  O[d, col]      += sum_token code_v[token, d] * (p[token, col] * vscale[token, g(d)])
+// The codes enter the MMA as exact integers at no conversion cost: a nibble (or a
+// whole byte, even nibble + 16 x odd nibble) masked in place inside an fp16 lane IS
+// the fp16 subnormal value * 2^-24.  The mix of two nibbles in a byte is resolved by
+// the other operand (scores: the q slots are q_even - q_odd/16 and q_odd/16) or in the
+// epilogue (output: odd row = (mixed row - even row) / 16), the power of two likewise.
+// int8 codes are biased to unsigned and byte-permuted into the low mantissa bits the
+// same way.  Scale and zero-point
+// are applied per group outside the MMA:
+//   s = sum_g kscale_g * S_g + kzero_g * sum_{d in g} q[d]
+//   o += sum_token p * vzero_g   (accumulated on CUDA cores)
+// With at most 4 q heads per kv head the 8 MMA columns carry a hi/lo fp16 split
+// of q (and of p * vscale), so the products are accurate to ~2^-22; with 5..8
+// q heads the columns are the heads themselves and q, p are rounded to fp16.
+// Accumulation is fp32 throughout.
+//
+// Softmax is the usual online recurrence in the log2 domain, one 16-token tile
+// per warp per stage; accumulators are rescaled only when a running maximum
+// moves.  The partial written per (sequence, q head, split) is (m, l, o) with m
+// in the natural-log domain and o un-normalised.
+//
+// Synchronisation on the default path is cp.async group completion and
+// __syncthreads only; no CTA ever waits for another.  The TMA staging option waits on
+// "stage landed" mbarriers of its own CTA, every wait bounded (a wait that runs out sets
+// the device status word and ends the CTA).
+//
+// This kernel cuts every sequence into a FIXED number of splits (the caller's n_splits),
+// one CTA each, and writes one partial per split in a public layout; it serves
+// knlp_b200_decode_splitk.  The default decode path of the library is the balanced kernel
+// of decode_dq_kernel.cuh, which shares this math and hands the work out inside the launch.
+//
+// Included by the host file (which only declares the instantiations) and by one small
+// translation unit per pair of K/V modes, so the instantiations compile in parallel.
 #pragma once
 
 #include <atomic>
@@ -1017,9 +1071,15 @@ template <int HD, int KMODE, int VMODE>
 int launch_split(const DecodeArgs& a, const MmaParams& mp, bool split, const TmaMaps* tm,
                  cudaStream_t st) {
   static const TmaMaps none{};
-  if (tm) {
-    return split ? launch_inst<HD, KMODE, VMODE, true, true>(a, mp, *tm, st)
-                 : launch_inst<HD, KMODE, VMODE, false, true>(a, mp, *tm, st);
+  // TMA staging is compiled for the INT4 caches and for INT8 K with asymmetric INT4 V; the
+  // other mode pairs are always staged with cp.async
+  constexpr bool kTmaBuilt = VMODE != KNLP_KV_INT8_G32 &&
+                             !(KMODE == KNLP_KV_INT8_G32 && VMODE == KNLP_KV_INT4_SYM);
+  if constexpr (kTmaBuilt) {
+    if (tm) {
+      return split ? launch_inst<HD, KMODE, VMODE, true, true>(a, mp, *tm, st)
+                   : launch_inst<HD, KMODE, VMODE, false, true>(a, mp, *tm, st);
+    }
   }
   return split ? launch_inst<HD, KMODE, VMODE, true, false>(a, mp, none, st)
                : launch_inst<HD, KMODE, VMODE, false, false>(a, mp, none, st);
