@@ -94,16 +94,21 @@ typedef struct {
 /* Flags for knlp_b200_decode_splitk. */
 #define KNLP_DECODE_FORCE_GENERIC 1u /* use the stride-generic CUDA-core kernel */
 #define KNLP_DECODE_USE_TMA 2u       /* stage with TMA tensor copies + mbarriers instead of cp.async */
+/* Test aid, with KNLP_DECODE_USE_TMA only: the first stage of every CTA announces 16 bytes
+ * more than it copies, so the bounded wait on it runs out (about 2 ms); the kernel then
+ * writes empty partials, sets the status word read by knlp_b200_debug_status and returns.
+ * It exercises the give-up path without any fault: every copy that is issued lands. */
+#define KNLP_DECODE_DEBUG_STALL 16u
 
 /* ABI version of the loaded library (KNLP_B200_ABI_VERSION at build time). */
 int knlp_b200_abi_version(void);
 
 /*
  * Debug aid, no counterpart in the reference.  The decode kernel bounds every
- * barrier wait; if one ever runs out it sets a device-side status word and ends
- * (its partials are then garbage).  This call SYNCHRONISES the current device,
- * returns the word (0 = clean, 1 = a wait ran out, -1 = could not be read) and
- * clears it.  Not for use on a hot path or during stream capture.
+ * barrier wait (2 ms); if one ever runs out it sets a device-side status word, reports
+ * the split as empty and ends (the attention output is then wrong, not garbage).  This
+ * call SYNCHRONISES the current device, returns the word (0 = clean, 1 = a wait ran out,
+ * -1 = could not be read) and clears it.  Not for use on a hot path or during capture.
  */
 int knlp_b200_debug_status(void);
 

@@ -23,6 +23,7 @@ DECODE_FORCE_GENERIC = 1
 DECODE_USE_TMA = 2
 DECODE_EMIT_PARTIAL = 4
 DECODE_FIXED_SPLITS = 8
+DECODE_DEBUG_STALL = 16
 
 SYMBOLS = (
     "knlp_b200_abi_version",

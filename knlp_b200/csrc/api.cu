@@ -198,7 +198,8 @@ int decode_args(const void* query, int q_dtype, const int64_t q_stride[2],
 int launch_splitk(const DecodeArgs& a, unsigned flags, cudaStream_t st) {
   int rc = 1;
   if (!(flags & KNLP_DECODE_FORCE_GENERIC)) {
-    rc = launch_decode_mma(a, (flags & KNLP_DECODE_USE_TMA) != 0, st);
+    rc = launch_decode_mma(a, (flags & KNLP_DECODE_USE_TMA) != 0,
+                           (flags & KNLP_DECODE_DEBUG_STALL) != 0, st);
     if (rc <= 0) return rc;  // launched, or failed for good
   }
   return launch_decode_generic(a, st);

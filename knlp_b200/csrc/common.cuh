@@ -110,7 +110,8 @@ int launch_decode_generic(const DecodeArgs& a, cudaStream_t st);
 // Returns KNLP_OK if it launched, 1 if the shape/strides are not eligible for the
 // tensor-core kernel (caller falls back to the generic one), <0 on error.
 // allow_tma = false keeps the tensor-core kernel on its cp.async loader.
-int launch_decode_mma(const DecodeArgs& a, bool allow_tma, cudaStream_t st);
+// debug_stall: test aid of the TMA staging, see KNLP_DECODE_DEBUG_STALL.
+int launch_decode_mma(const DecodeArgs& a, bool allow_tma, bool debug_stall, cudaStream_t st);
 // Shape / layout test of the tensor-core kernels: 0 = eligible (heads per CTA and page
 // size filled in as log2), 1 = generic kernel only.
 int decode_mma_layout(const DecodeArgs& a, int* hpb_log2, int* page_log2);

@@ -309,8 +309,9 @@ int decode_mma_layout(const DecodeArgs& a, int* hpb_log2_out, int* page_log2_out
   return 0;
 }
 
-int launch_decode_mma(const DecodeArgs& a, bool allow_tma, cudaStream_t st) {
+int launch_decode_mma(const DecodeArgs& a, bool allow_tma, bool debug_stall, cudaStream_t st) {
   MmaParams mp{};
+  mp.debug_stall = debug_stall ? 1 : 0;
   if (decode_mma_layout(a, &mp.hpb_log2, &mp.page_log2)) return 1;
   // the page-id ring of the kernel holds 16 ids per stage; a stage is (warps / heads per
   // CTA) * 16 tokens, so blocks of 1 or 2 tokens can need more: the generic kernel takes those

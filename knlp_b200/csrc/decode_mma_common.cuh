@@ -99,13 +99,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after kSpinLimit polls (each poll itself blocks for a
-// hardware-defined time), so a lost completion ends the kernel instead of hanging it.
-constexpr int kSpinLimit = 1 << 20;
+// Bounded wait: gives up after kWaitLimitNs of wall time (the %globaltimer), so a lost
+// completion ends the kernel within milliseconds instead of hanging it.
+constexpr unsigned long long kWaitLimitNs = 2000000ull;
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (int i = 0; i < kSpinLimit; ++i) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_ns();
+  do {
     if (mbar_try_wait(bar, parity)) return true;
-  }
+  } while (global_ns() - t0 < kWaitLimitNs);
   return false;
 }
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, uint32_t bar, int c0,
@@ -247,6 +254,7 @@ struct MmaParams {
   int hpb_log2;   // kv heads per CTA = 1 << hpb_log2
   int page_log2;  // block_size = 1 << page_log2
   int* status;    // device status word: set to 1 by a kernel whose bounded wait ran out
+  int debug_stall;  // test aid (TMA staging): the first stage announces more bytes than it copies
 };
 
 // Calls f(it0 + S, integral_constant<S>) for S = FIRST .. N-1 while it0 + S < n; stops

@@ -451,7 +451,11 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
     const int stage_tok0 = start + it * TT;
     const int live_tiles = min(tiles, (end - stage_tok0 + 15) >> 4);
     const uint32_t full = bar0 + sn * 8;
-    if (lane == 0) mbar_arrive_expect_tx(full, static_cast<uint32_t>(live_tiles) * tile_bytes);
+    // (debug_stall: 16 bytes that never come, so that the bounded wait on this stage runs
+    // out; every copy that IS issued still lands)
+    if (lane == 0)
+      mbar_arrive_expect_tx(full, static_cast<uint32_t>(live_tiles) * tile_bytes +
+                                      ((mp.debug_stall && it == 0) ? 16u : 0u));
     __syncwarp();
     const uint32_t stage_base = smem_base + static_cast<uint32_t>(sn) * G::kStageBytes;
 #pragma unroll
@@ -909,6 +913,25 @@ decode_mma_kernel(const DecodeArgs a, const MmaParams mp, const __grid_constant_
 
   // ---------------- epilogue: reduce lanes, merge the warps of a head, write ----
   cp_async_wait<0>();
+  if constexpr (TMA) {
+    // A wait ran out in some warp (never expected; the status word is set): the stage
+    // buffers may still be the target of copies, so they are not reused; this split
+    // reports no tokens and the CTA ends.
+    if (__syncthreads_or(lost ? 1 : 0)) {
+      const int heads = HPB * n_rep;
+      for (int i = tid; i < heads * HD; i += kThreads) {
+        const int hh = i / HD, e = i % HD;
+        const int64_t row = static_cast<int64_t>(seq) * a.n_q_heads + hb * HPB * n_rep + hh;
+        const int64_t pidx = row * a.n_splits + split;
+        a.part_o[pidx * HD + e] = 0.0f;
+        if (e == 0) {
+          a.part_m[pidx] = -INFINITY;
+          a.part_l[pidx] = 0.0f;
+        }
+      }
+      return;
+    }
+  }
   __syncthreads();  // all stages consumed; shared memory is reused below
 
   // per-warp totals over the 8 fragment rows

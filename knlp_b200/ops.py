@@ -234,6 +234,8 @@ def _decode_flags(force_generic) -> int:
     selectable); True = stride-generic CUDA-core kernel."""
     if force_generic == "tma":
         return _lib.DECODE_USE_TMA
+    if force_generic == "tma_stall":  # test aid: makes the kernel's bounded wait run out
+        return _lib.DECODE_USE_TMA | _lib.DECODE_DEBUG_STALL
     return _lib.DECODE_FORCE_GENERIC if force_generic else 0
 
 

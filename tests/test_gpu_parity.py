@@ -415,6 +415,26 @@ def test_context_shard_on_one_gpu(world, cuda_device):
         assert_close(out.cpu().numpy(), ref, f"context shard x{world}")
 
 
+def test_bounded_wait_gives_up_and_reports(cuda_device):
+    """The TMA staging waits on its "stage landed" barriers for at most 2 ms.  With the test
+    flag the first stage of every CTA announces 16 bytes that never come (every copy that is
+    issued still lands, nothing faults): the wait runs out, the kernel reports its splits as
+    empty, sets the status word and RETURNS; the context stays usable."""
+    from knlp_b200 import ops, workloads
+    w = workloads.build("stall", n_seqs=2, n_q_heads=32, n_kv_heads=8, head_dim=128,
+                        seq_lens=[300, 100], seed=3, device=cuda_device)
+    ref = _workload_oracle(w)
+    assert ops.device_status() == 0
+    out = w.decode(out_dtype=torch.float32, force_generic="tma_stall", n_splits=2)
+    assert ops.device_status() == 1      # synchronises: the kernel came back
+    assert ops.device_status() == 0      # reading it cleared it
+    assert torch.isfinite(out).all()     # empty splits, not garbage
+    # and the same launch without the flag is right again
+    out = w.decode(out_dtype=torch.float32, force_generic="tma", n_splits=2)
+    assert_close(out.cpu().numpy(), ref, "after a give-up")
+    assert ops.device_status() == 0
+
+
 def test_zz_device_status_is_clean(cuda_device):
     """No kernel of this session gave up on a barrier wait."""
     from knlp_b200 import ops

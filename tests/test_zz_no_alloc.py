@@ -27,7 +27,7 @@ def _planes(w):
     return kp, vp
 
 
-def _noalloc(w, out, n_splits=0):
+def _noalloc(w, out, n_splits=0, out_dtype=None):
     """One raw C-ABI call on torch's current stream; returns the status code."""
     from knlp_b200 import _lib, ops, workloads
     lib = _lib.load()
@@ -40,7 +40,8 @@ def _noalloc(w, out, n_splits=0):
             w.query.data_ptr(), ops._dt(w.query), ops._stride2(w.query), C.byref(kp), C.byref(vp),
             w.block_table.data_ptr(), w.block_table.stride(0), w.seq_lens.data_ptr(),
             int(w.key_cache.shape[0]), S, Hq, w.n_kv_heads, d, page, n_splits, max_len,
-            out.data_ptr(), _lib.F32, d, torch.cuda.current_stream(w.query.device).cuda_stream)
+            out.data_ptr(), _lib.F32 if out_dtype is None else out_dtype, d,
+            torch.cuda.current_stream(w.query.device).cuda_stream)
 
 
 def _check(out, ref, what):
@@ -100,6 +101,10 @@ def test_noalloc_rejects_what_the_array_cannot_hold(cuda_device):
     assert b"capacity" in _lib.load().knlp_b200_strerror(rc).lower() or \
         b"large" in _lib.load().knlp_b200_strerror(rc).lower()
     assert torch.all(out == 7.0)               # nothing was launched
+    # an output type the merge would refuse is refused before anything is launched, too
+    rc = _noalloc(w, out, n_splits=2, out_dtype=99)
+    torch.cuda.synchronize()
+    assert rc < 0 and torch.all(out == 7.0)
     # the largest count that fits is accepted and right
     assert _noalloc(w, out, n_splits=too_many - 1) == 0
     torch.cuda.synchronize()
