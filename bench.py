@@ -711,6 +711,21 @@ def teardown(torch, dist, world):
         dist.destroy_process_group()
 
 
+def run_append_loop(args):
+    """Side measurement: the append-then-attend loop of a workload (benchmark configuration
+    5 is mixed_k8v4), with the append as its own launch and fused into the decode launch."""
+    import torch
+    from knlp_b200 import ops, workloads
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    peak_gbs, _ = peaks()
+    for fused in (False, True):
+        row = measure_append_loop(torch, ops, workloads, args.workload, dev, max(args.steps, 20),
+                                  args.warmup, torch.cuda.synchronize, peak_gbs, fused=fused)
+        print(json.dumps(row), flush=True)
+        torch.cuda.empty_cache()
+
+
 def run_write_path(args):
     """Side measurement, not the headline: the quantize-and-append kernel over a prefill-sized
     batch (tokens x 8 kv heads x 128, bf16, K and V), algorithmic read + write bytes per
@@ -773,12 +788,16 @@ def main():
                     help="short run for use under ncu: timed steps only, one JSON line of timings")
     ap.add_argument("--e2e-eager", action="store_true",
                     help="end-to-end leg as eager operator calls instead of one replayed CUDA graph")
+    ap.add_argument("--append-loop", action="store_true",
+                    help="time 64 append+attend steps of --workload, append separate and fused")
     ap.add_argument("--write-path", action="store_true",
                     help="time the quantize-and-append kernel instead (side measurement)")
     args = ap.parse_args()
     shape_of(args.workload)  # unknown workloads are refused up front
     if args.write_path:
         run_write_path(args)
+    elif args.append_loop:
+        run_append_loop(args)
     elif args.impl == "reference":
         run_reference(args)
     else:

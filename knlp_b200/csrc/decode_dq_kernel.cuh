@@ -240,6 +240,42 @@ __device__ __noinline__ void merge_pair(const float* pm, const float* pl, const 
   }
 }
 
+// Four consecutive elements (index a multiple of 4) of a row of runtime dtype, with one
+// vector load where the address allows it.
+__device__ __forceinline__ void load4_rt(const void* base, int64_t idx, int dt, float out[4]) {
+  if (dt == KNLP_F32) {
+    const float* p = static_cast<const float*>(base) + idx;
+    if ((reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+      const float4 v = __ldg(reinterpret_cast<const float4*>(p));
+      out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) out[i] = __ldg(p + i);
+    }
+    return;
+  }
+  const uint16_t* p = static_cast<const uint16_t*>(base) + idx;
+  uint32_t w0, w1;
+  if ((reinterpret_cast<uintptr_t>(p) & 7) == 0) {
+    const uint2 v = __ldg(reinterpret_cast<const uint2*>(p));
+    w0 = v.x;
+    w1 = v.y;
+  } else {
+    w0 = __ldg(p) | (static_cast<uint32_t>(__ldg(p + 1)) << 16);
+    w1 = __ldg(p + 2) | (static_cast<uint32_t>(__ldg(p + 3)) << 16);
+  }
+  if (dt == KNLP_F16) {
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&w0));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&w1));
+    out[0] = a.x; out[1] = a.y; out[2] = b.x; out[3] = b.y;
+  } else {  // bf16: the upper half of an fp32
+    out[0] = __uint_as_float(w0 << 16);
+    out[1] = __uint_as_float(w0 & 0xFFFF0000u);
+    out[2] = __uint_as_float(w1 << 16);
+    out[3] = __uint_as_float(w1 & 0xFFFF0000u);
+  }
+}
+
 // The step's new token of one (sequence, kv head), done by ONE warp of the pair's last
 // member: quantize K and V with the write path's own arithmetic (quant_row.cuh), store
 // them at the token's slot, and leave what the attention needs of it in shared memory -
@@ -260,10 +296,15 @@ __device__ __noinline__ void append_token(const void* ksrc, const void* vsrc, co
   float x[4] = {0.0f, 0.0f, 0.0f, 0.0f};
   int c[4];
   float sc, mn;
-  // ---- key
+  // ---- key (the value row and the q rows are fetched up front as well)
+  float xv[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  float qv[8][4];
   if (active) {
+    load4_rt(ksrc, e0, src_dt, x);
+    load4_rt(vsrc, e0, src_dt, xv);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) x[i] = load_elem_rt(ksrc, e0 + i, src_dt);
+    for (int hs = 0; hs < 8; ++hs)
+      if (hs < n_rep) load4_rt(q, q_row0 + hs * q_head_stride + e0, q_dt, qv[hs]);
   }
   quantize4(KMODE, x, lane, clip_ratio, c, sc, mn);
   if (active) store_quantized4(KMODE, c, sc, mn, k_crow, k_srow, k_zrow, e0, leader, true);
@@ -277,24 +318,22 @@ __device__ __noinline__ void append_token(const void* ksrc, const void* vsrc, co
       kh[i] = active ? code * s16 + z16 : 0.0f;
     }
     const float mul = rsqrtf(static_cast<float>(HD)) * 1.4426950408889634f;  // log2 domain
-    for (int hs = 0; hs < n_rep; ++hs) {
-      float dot = 0.0f;
-      if (active) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
-          dot = fmaf(load_elem_rt(q, q_row0 + hs * q_head_stride + e0 + i, q_dt), kh[i], dot);
+    for (int hs = 0; hs < 8; ++hs) {
+      if (hs < n_rep) {
+        float dot = 0.0f;
+        if (active) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) dot = fmaf(qv[hs][i], kh[i], dot);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        if (lane == 0) s_new[hs] = dot * mul;
       }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-      if (lane == 0) s_new[hs] = dot * mul;
     }
   }
   // ---- value
-  if (active) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) x[i] = load_elem_rt(vsrc, e0 + i, src_dt);
-  }
-  quantize4(VMODE, x, lane, clip_ratio, c, sc, mn);
+  quantize4(VMODE, xv, lane, clip_ratio, c, sc, mn);
   if (active) {
     store_quantized4(VMODE, c, sc, mn, v_crow, v_srow, v_zrow, e0, leader, true);
     const float s16 = __half2float(__float2half_rn(sc));
@@ -335,6 +374,10 @@ decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
   // here meanwhile (they would otherwise hold registers the loop needs)
   __shared__ int s_park[12];
   __shared__ float s_mrow[HPB * 8], s_irow[HPB * 8];  // merge: row maximum and weight scale
+  // the step's new token of the pair (its last member only): scaled scores of the q rows
+  // (log2 domain) and the dequantized value rows, from the prologue to the epilogue
+  __shared__ float sm_snew[HPB * 8];
+  __shared__ __align__(16) float sm_vnew[HPB * HD];
 
   const int tid = threadIdx.x;
   const int lane = tid & 31;
@@ -705,6 +748,31 @@ decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
         return true;
       };
       run_stages<0, kStages - 1, false>(first_fill, 0, kStages);
+    }
+
+    // ---------------- the step's new token (the pair's last member): while the first
+    // copies are in flight, one warp per kv head quantizes it, stores it and leaves its
+    // scores and value row in shared memory for the epilogue ----------------
+    if (has_new && w_tile == 0) {
+      const int kvh_e = hb * HPB + w_head;
+      int blk = __ldg(bt_row + (len >> dp.page_log2));
+      blk = blk < 0 ? 0 : (blk > max_blk ? max_blk : blk);
+      const int off = len & page_mask;
+      auto row = [&](auto* base, const int64_t* st) {
+        return base + (static_cast<int64_t>(blk) * st[0] + static_cast<int64_t>(off) * st[1] +
+                       static_cast<int64_t>(kvh_e) * st[2]);
+      };
+      const int esz = dp.new_dtype == KNLP_F32 ? 4 : 2;
+      append_token<HD, KMODE, VMODE>(
+          static_cast<const uint8_t*>(dp.new_key) +
+              (seq * dp.nk_stride[0] + kvh_e * dp.nk_stride[1]) * esz,
+          static_cast<const uint8_t*>(dp.new_value) +
+              (seq * dp.nv_stride[0] + kvh_e * dp.nv_stride[1]) * esz,
+          dp.new_dtype, row(a.k.codes, a.k.cs), row(a.k.scales, a.k.ss),
+          kAsymK ? row(a.k.zeros, a.k.zs) : nullptr, row(a.v.codes, a.v.cs),
+          row(a.v.scales, a.v.ss), kAsymV ? row(a.v.zeros, a.v.zs) : nullptr, a.q, a.q_dtype,
+          static_cast<int64_t>(seq) * a.q_stride[0] + kvh_e * n_rep * a.q_stride[1],
+          a.q_stride[1], n_rep, dp.clip_ratio, sm_snew + w_head * 8, sm_vnew + w_head * HD);
     }
 
     // ---------------- q fragments (B operand), kept in registers ----------------
@@ -1167,32 +1235,8 @@ decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
         }
       }
     }
-    // the step's new token (the pair's last member only): one warp per kv head of the pair
-    float* sm_snew = sm_l + kWarpsCta * kHeadSlots;  // [HPB][8] scaled scores, log2 domain
-    float* sm_vnew = sm_snew + HPB * 8;              // [HPB][HD] dequantized value rows
+    // the step's new token was quantized, stored and scored in the prologue (sm_snew, sm_vnew)
     const bool new_here = appending && s_park[0] - s_park[1] == s_park[2] - 1;
-    if (new_here && w_tile == 0) {
-      const int seq_e = s_park[3], kvh_e = s_park[4] * HPB + w_head;
-      const int len_e = __ldg(a.seq_lens + seq_e);
-      int blk = __ldg(a.block_table + static_cast<int64_t>(seq_e) * a.bt_stride +
-                      (len_e >> dp.page_log2));
-      blk = blk < 0 ? 0 : (blk > max_blk ? max_blk : blk);
-      const int off = len_e & page_mask;
-      auto row = [&](const Plane& pl, auto* base, const int64_t* st) {
-        return base + (static_cast<int64_t>(blk) * st[0] + static_cast<int64_t>(off) * st[1] +
-                       static_cast<int64_t>(kvh_e) * st[2]);
-      };
-      append_token<HD, KMODE, VMODE>(
-          static_cast<const uint8_t*>(dp.new_key) +
-              (seq_e * dp.nk_stride[0] + kvh_e * dp.nk_stride[1]) * (dp.new_dtype == KNLP_F32 ? 4 : 2),
-          static_cast<const uint8_t*>(dp.new_value) +
-              (seq_e * dp.nv_stride[0] + kvh_e * dp.nv_stride[1]) * (dp.new_dtype == KNLP_F32 ? 4 : 2),
-          dp.new_dtype, row(a.k, a.k.codes, a.k.cs), row(a.k, a.k.scales, a.k.ss),
-          kAsymK ? row(a.k, a.k.zeros, a.k.zs) : nullptr, row(a.v, a.v.codes, a.v.cs),
-          row(a.v, a.v.scales, a.v.ss), kAsymV ? row(a.v, a.v.zeros, a.v.zs) : nullptr, a.q,
-          a.q_dtype, static_cast<int64_t>(seq_e) * a.q_stride[0] + kvh_e * n_rep * a.q_stride[1],
-          a.q_stride[1], n_rep, dp.clip_ratio, sm_snew + w_head * 8, sm_vnew + w_head * HD);
-    }
     __syncthreads();
     // this CTA's partial of the pair: rows (kv head hl, q head hs), merged over the tiles
     {
