@@ -264,6 +264,35 @@ int knlp_b200_decode_append_attention(const void* query, int q_dtype, const int6
                                       void* stream);
 
 /*
+ * Routed (block-sparse) decode over the packed cache: every kv head of every sequence
+ * attends to its OWN list of selected cache blocks, all tokens of a selected block count.
+ * Same contract as fused_routed_decode of the reference (routing/fused_routed_attention.py
+ * :425-492, kernel :45-190), which reads an unquantized cache; this one reads the packed
+ * planes of this library through the loader of knlp_b200_decode_attention.
+ *   block_tables  int32, row s * n_kv_heads + h (row stride bt_stride elements) lists the
+ *                 selected physical blocks of kv head h of sequence s
+ *   block_counts  int32 [n_seqs * n_kv_heads]: valid entries of each row (0: the q heads
+ *                 of that kv head get zeros, as in the reference)
+ *   query         [n_seqs, n_q_heads, head_dim], q_stride[0] == n_q_heads * q_stride[1]
+ *   workspace / counters: as knlp_b200_decode_attention, sized by
+ *                 knlp_b200_decode_workspace(n_seqs * n_kv_heads, n_q_heads / n_kv_heads, 1,
+ *                 head_dim, block_size, max_selected_blocks * block_size, ...)
+ *   flags         0 or KNLP_DECODE_EMIT_PARTIAL
+ * One launch.  Only layouts the balanced tensor-core kernel addresses (head_dim 64 / 128,
+ * block_size a power of two >= 16, both planes quantized): others return KNLP_ERR_STRIDE.
+ */
+int knlp_b200_routed_decode_attention(const void* query, int q_dtype, const int64_t q_stride[2],
+                                      const knlp_kv_plane* k_plane, const knlp_kv_plane* v_plane,
+                                      const int32_t* block_tables, int64_t bt_stride,
+                                      const int32_t* block_counts, int64_t num_blocks,
+                                      int n_seqs, int n_q_heads, int n_kv_heads, int head_dim,
+                                      int block_size, int max_selected_blocks,
+                                      float* workspace, int64_t workspace_floats,
+                                      int32_t* counters, int64_t counter_ints,
+                                      void* out, int out_dtype, int64_t out_row_stride,
+                                      unsigned flags, void* stream);
+
+/*
  * Merge n_parts partials per (sequence, q head) row.  No counterpart function
  * in the reference: the algebra is its in-loop online-softmax recurrence
  * (:808-815, :883-887) applied across splits.

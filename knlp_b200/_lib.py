@@ -35,6 +35,7 @@ SYMBOLS = (
     "knlp_b200_decode_attention",
     "knlp_b200_decode_workspace",
     "knlp_b200_decode_append_attention",
+    "knlp_b200_routed_decode_attention",
     "knlp_b200_combine",
     "knlp_b200_decode_noalloc",
     "knlp_b200_plugin_quantize",
@@ -119,6 +120,12 @@ def load() -> C.CDLL:
         C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
         C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int, C.c_int64,
         C.c_uint, C.POINTER(NewTokens), C.c_void_p]
+    lib.knlp_b200_routed_decode_attention.restype = C.c_int
+    lib.knlp_b200_routed_decode_attention.argtypes = [
+        C.c_void_p, C.c_int, I64P, PL, PL, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
+        C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+        C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int, C.c_int64,
+        C.c_uint, C.c_void_p]
     lib.knlp_b200_decode_workspace.restype = C.c_int
     lib.knlp_b200_decode_workspace.argtypes = [
         C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,

@@ -285,7 +285,7 @@ int knlp_b200_decode_append_attention(const void* query, int q_dtype, const int6
   }
   if (!(flags & (KNLP_DECODE_FORCE_GENERIC | KNLP_DECODE_USE_TMA | KNLP_DECODE_FIXED_SPLITS))) {
     rc = launch_decode_dq(a, workspace, workspace_floats, counters, counter_ints, max_seq_len, emit,
-                          sm_count(), new_tokens, st);
+                          sm_count(), new_tokens, false, st);
     if (rc <= 0) return rc;  // launched, or failed for good
   }
   // a layout only the other kernels can address: they do not append
@@ -327,6 +327,44 @@ int knlp_b200_decode_attention(const void* query, int q_dtype, const int64_t q_s
       n_seqs, n_q_heads, n_kv_heads, head_dim, block_size, max_seq_len, workspace,
       workspace_floats, counters, counter_ints, out, out_dtype, out_row_stride, flags, nullptr,
       stream);
+}
+
+int knlp_b200_routed_decode_attention(const void* query, int q_dtype, const int64_t q_stride[2],
+                                      const knlp_kv_plane* k_plane, const knlp_kv_plane* v_plane,
+                                      const int32_t* block_tables, int64_t bt_stride,
+                                      const int32_t* block_counts, int64_t num_blocks, int n_seqs,
+                                      int n_q_heads, int n_kv_heads, int head_dim, int block_size,
+                                      int max_selected_blocks, float* workspace,
+                                      int64_t workspace_floats, int32_t* counters,
+                                      int64_t counter_ints, void* out, int out_dtype,
+                                      int64_t out_row_stride, unsigned flags, void* stream) {
+  if (!out || !workspace || !counters) return KNLP_ERR_NULL;
+  if (!dtype_ok(out_dtype)) return KNLP_ERR_DTYPE;
+  if (flags & ~KNLP_DECODE_EMIT_PARTIAL) return KNLP_ERR_MODE;
+  const bool emit = (flags & KNLP_DECODE_EMIT_PARTIAL) != 0;
+  if (emit && out_dtype != KNLP_F32) return KNLP_ERR_DTYPE;
+  if (max_selected_blocks < 0 || block_size <= 0 ||
+      static_cast<int64_t>(max_selected_blocks) * block_size > 0x7fffffff)
+    return KNLP_ERR_SHAPE;
+  const int max_len = max_selected_blocks * block_size;
+  DecodeArgs a;
+  int rc = decode_args(query, q_dtype, q_stride, k_plane, v_plane, block_tables, bt_stride,
+                       block_counts, num_blocks, n_seqs, n_q_heads, n_kv_heads, head_dim,
+                       block_size, max_len, &a);
+  if (rc) return rc < 0 ? rc : KNLP_OK;
+  a.out = out;
+  a.out_dtype = out_dtype;
+  a.out_row_stride = out_row_stride;
+  const uintptr_t mis = reinterpret_cast<uintptr_t>(workspace) % 16;
+  if (mis % 4) return KNLP_ERR_STRIDE;
+  if (mis) {
+    workspace += (16 - mis) / 4;
+    workspace_floats -= (16 - mis) / 4;
+  }
+  rc = launch_decode_dq(a, workspace, workspace_floats, counters, counter_ints, max_len, emit,
+                        sm_count(), nullptr, true, static_cast<cudaStream_t>(stream));
+  // only layouts of the balanced tensor-core kernel are served
+  return rc > 0 ? KNLP_ERR_STRIDE : rc;
 }
 
 int knlp_b200_combine(const float* part_m, const float* part_l, const float* part_o,

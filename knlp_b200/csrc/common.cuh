@@ -126,10 +126,11 @@ constexpr int kDecodeCtasPerSm = 16 / kDecodeWarps;
 // Balanced one-launch decode (decode_dq_kernel.cuh): a.out receives the attention output
 // (emit_partial: fp32 rows [o un-normalised, m, l]).  ws / ints: the workspace sized by
 // dq_workspace_size; the ints are counters that must be zero on entry and are left zero.  Returns KNLP_OK, 1 if the call is not eligible (nothing launched),
-// <0 on error.
+// <0 on error.  per_head_tables: routed decode - block_table and seq_lens have one row /
+// entry per (sequence, kv head), the lengths count whole blocks.
 int launch_decode_dq(const DecodeArgs& a, float* ws, int64_t ws_floats, int* ints, int64_t n_ints,
                      int max_seq_len, bool emit_partial, int n_sms,
-                     const knlp_new_tokens* new_tokens, cudaStream_t st);
+                     const knlp_new_tokens* new_tokens, bool per_head_tables, cudaStream_t st);
 void dq_workspace_size(int n_seqs, int n_q_heads, int n_kv_heads, int head_dim, int n_sms,
                        int64_t* floats, int64_t* ints);
 // Device-side status word of the decode kernels (0 = clean); synchronises.

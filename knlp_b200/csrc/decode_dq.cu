@@ -59,11 +59,27 @@ void dq_workspace_size(int n_seqs, int n_q_heads, int n_kv_heads, int head_dim, 
   *ints = 2 * n_pairs;  // ticket and arrival counters
 }
 
-int launch_decode_dq(const DecodeArgs& a, float* ws, int64_t ws_floats, int* ints, int64_t n_ints,
-                     int max_seq_len, bool emit_partial, int n_sms,
-                     const knlp_new_tokens* nt, cudaStream_t st) {
+int launch_decode_dq(const DecodeArgs& a_in, float* ws, int64_t ws_floats, int* ints,
+                     int64_t n_ints, int max_seq_len, bool emit_partial, int n_sms,
+                     const knlp_new_tokens* nt, bool per_head_tables, cudaStream_t st) {
   DqParams dp{};
-  if (decode_mma_layout(a, &dp.hpb_log2, &dp.page_log2)) return 1;
+  if (decode_mma_layout(a_in, &dp.hpb_log2, &dp.page_log2)) return 1;
+  DecodeArgs a = a_in;
+  if (per_head_tables) {
+    // Every (sequence, kv head) becomes a sequence of its own with one kv head: row
+    // s * n_kv_heads + h of the tables, of the lengths (given in blocks), of q and of out.
+    if (nt) return KNLP_ERR_MODE;
+    const int n_rep = a.n_q_heads / a.n_kv_heads;
+    if (a.q_stride[0] != static_cast<int64_t>(a.n_q_heads) * a.q_stride[1]) return 1;
+    if (static_cast<int64_t>(a.n_seqs) * a.n_kv_heads > 0x7fffffff) return 1;
+    dp.vheads = a.n_kv_heads;
+    dp.len_shift = dp.page_log2;
+    dp.hpb_log2 = 0;
+    a.n_seqs *= a.n_kv_heads;
+    a.n_q_heads = n_rep;
+    a.n_kv_heads = 1;
+    a.q_stride[0] = n_rep * a.q_stride[1];
+  }
   // q rows are fetched with 16-byte loads
   const int q_align = a.q_dtype == KNLP_F32 ? 4 : 8;
   if (reinterpret_cast<uintptr_t>(a.q) % 16 || a.q_stride[0] % q_align || a.q_stride[1] % q_align)

@@ -56,6 +56,13 @@ struct DqParams {
   int64_t nk_stride[2], nv_stride[2];
   int new_dtype;
   float clip_ratio;
+  // Per-kv-head page tables (routed decode).  vheads > 0: the launch sees every (sequence,
+  // kv head) as a sequence of its own with ONE kv head - row v of block_table / seq_lens /
+  // query / out belongs to kv head v % vheads of a cache that holds vheads heads per token
+  // (heads per CTA is 1 then).  len_shift: seq_lens count 1 << len_shift tokens each
+  // (lengths given in whole blocks).
+  int vheads;
+  int len_shift;
 };
 
 namespace {
@@ -346,9 +353,10 @@ __device__ __noinline__ void append_token(const void* ksrc, const void* vsrc, co
   }
 }
 
-template <int HD, int KMODE, int VMODE, bool SPLIT, int HPBL>
+template <int HD, int KMODE, int VMODE, bool SPLIT, int HPBL, bool ROUTED = false>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
+  static_assert(!ROUTED || HPBL == 0, "per-kv-head page tables: one kv head per CTA");
   using G = Geo<HD, KMODE, VMODE, kTilePad>;
   constexpr int kStages = G::kStages;
   constexpr bool kInt8V = G::kInt8V;
@@ -397,7 +405,7 @@ decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
   // a sequence without cached tokens still has work when the step appends one to it
   const bool appending = dp.new_key != nullptr;
   auto seq_chunks = [&](int s) -> int {
-    const int L = __ldg(a.seq_lens + s);
+    const int L = __ldg(a.seq_lens + s) << dp.len_shift;
     if (L < 0 || (L == 0 && !appending)) return 0;
     return L > CT ? (L + CT - 1) / CT : 1;
   };
@@ -476,6 +484,9 @@ decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
   const int max_blk = static_cast<int>(a.num_blocks) - 1;
   const uint32_t smem_base = smem_u32(smem);
   const float score_mul = rsqrtf(static_cast<float>(HD)) * 1.4426950408889634f * kTwo24;
+  // per-kv-head page tables: the heads of a token lie in different blocks, so the scale
+  // rows are fetched per (token, head), G::SB bytes a piece
+  constexpr bool routed = ROUTED;
   const bool page16 = dp.page_log2 == 4;
 
   // copy role: the 16-byte pieces of a stage are dealt to the threads in memory order
@@ -567,8 +578,9 @@ decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
     const int parts = parts_in;
     int* const ticket = dp.counters + (seq * HBn + hb);
     const int kvh = hb * HPB + w_head;
-    const int len = __ldg(a.seq_lens + seq);
+    const int len = __ldg(a.seq_lens + seq) << dp.len_shift;
     const int32_t* bt_row = a.block_table + static_cast<int64_t>(seq) * a.bt_stride;
+    const int hmem = hb + (routed ? seq % dp.vheads : 0);  // head block within the cache
     const int dyn0 = 2 * n_static;  // chunk of ticket 0
     if (tid == 0) {
       s_park[0] = slot;
@@ -611,15 +623,39 @@ decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
     const uint8_t* v_pp[kVPer];
 #pragma unroll
     for (int n = 0; n < kKPer; ++n)
-      k_pp[n] = a.k.codes + (hb * (G::KB << hpb_log2) + k_j * 16) +
+      k_pp[n] = a.k.codes + (hmem * (G::KB << hpb_log2) + k_j * 16) +
                 static_cast<uint32_t>((k_tt0 + n * k_dtt) & 15) * kcs1;
 #pragma unroll
     for (int n = 0; n < kVPer; ++n)
-      v_pp[n] = a.v.codes + (hb * (G::VB << hpb_log2) + v_j * 16) +
+      v_pp[n] = a.v.codes + (hmem * (G::VB << hpb_log2) + v_j * 16) +
                 static_cast<uint32_t>((v_tt0 + n * v_dtt) & 15) * vcs1;
     const uint8_t* s_pp = reinterpret_cast<const uint8_t*>(s_base) +
-                          (hb * s_tb + (s_tb >= 16 ? s_byte % s_tb : 0)) +
+                          (hmem * s_tb + (s_tb >= 16 ? s_byte % s_tb : 0)) +
                           static_cast<uint32_t>(s_tt & 15) * s_st1;
+
+    // routed: this thread's two scale pieces per stage - token tid % 64 of array tid / 64
+    // (K scales or K zeros) and of array 2 + tid / 64 (V scales or V zeros); the address
+    // within a block and the destination within a stage
+    const __half* r_base[2] = {nullptr, nullptr};
+    uint32_t r_st0[2] = {0u, 0u}, r_st1[2] = {0u, 0u}, r_dst[2] = {0u, 0u};
+    if constexpr (ROUTED) {
+      {
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+          const int arr = (tid >> 6) + 2 * n;
+          if ((arr == 1 && !kAsymK) || (arr == 3 && !kAsymV)) continue;
+          const Plane& pl = n ? a.v : a.k;
+          const __half* base = (arr & 1) ? pl.zeros : pl.scales;
+          const int64_t* st = (arr & 1) ? pl.zs : pl.ss;
+          r_base[n] = base + hmem * NG;
+          r_st0[n] = static_cast<uint32_t>(st[0]);
+          r_st1[n] = static_cast<uint32_t>(st[1]);
+          r_dst[n] = smem_base + (tid & 63) * G::SB +
+                     (arr == 0 ? G::kOffKs : arr == 1 ? G::kOffKz : arr == 2 ? G::kOffVs
+                                                                             : G::kOffVz);
+        }
+      }
+    }
 
     // page ids of a chunk: lane i of warp 0 fetches the i-th page the chunk touches
     auto load_pages = [&](int T) -> int {
@@ -659,6 +695,22 @@ decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
                                         static_cast<int64_t>(dt) * vcs1);
         cp_async16(v_dst[n] + stage_off, live ? src : a.v.codes, live ? 16 : 0);
       }
+      if constexpr (ROUTED) {
+        {
+          // one piece per (array, token): the scale row of this head alone
+          const int tok = stage_tok0 + (tid & 63);
+          const bool live = tok < len;
+          const uint32_t blk = live ? clamp_blk(pg_tab[ring][(tok >> dp.page_log2) - page0]) : 0u;
+#pragma unroll
+          for (int n = 0; n < 2; ++n) {
+            if (!r_base[n]) continue;
+            const __half* src = r_base[n] + (static_cast<int64_t>(blk) * r_st0[n] +
+                                             static_cast<int64_t>(tok & page_mask) * r_st1[n]);
+            cp_async_small<G::SB>(r_dst[n] + stage_off, live ? src : r_base[n], live ? G::SB : 0);
+          }
+          return;
+        }
+      }
       if (s_on) {
         const int tok = stage_tok0 + s_tt;
         const bool live = tok < len;
@@ -689,6 +741,17 @@ decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
       for (int n = 0; n < kKPer; ++n) cp_async16_full_at<stage_off>(k_dst[n], k_pp[n] + kb[n] * kcs0);
 #pragma unroll
       for (int n = 0; n < kVPer; ++n) cp_async16_full_at<stage_off>(v_dst[n], v_pp[n] + vb[n] * vcs0);
+      if constexpr (ROUTED) {
+        {
+          const uint64_t rb = clamp_blk(pg_tab[ring][pg0 + ((tid & 63) >> 4)]);
+#pragma unroll
+          for (int n = 0; n < 2; ++n)
+            if (r_base[n])
+              cp_async_small<G::SB>(r_dst[n] + stage_off,
+                                    r_base[n] + (rb * r_st0[n] + (tid & 15) * r_st1[n]), G::SB);
+          return;
+        }
+      }
       if (s_on) cp_async16_full_at<stage_off>(s_dst, s_pp + sb * s_st0);
     };
 
@@ -1352,11 +1415,11 @@ decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
   }
 }
 
-template <int HD, int KMODE, int VMODE, bool SPLIT, int HPBL>
+template <int HD, int KMODE, int VMODE, bool SPLIT, int HPBL, bool ROUTED = false>
 int launch_dq_hpb(const DecodeArgs& a, const DqParams& dp, cudaStream_t st) {
   using G = Geo<HD, KMODE, VMODE, kTilePad>;
   constexpr int kSmem = G::kSmemBytes + 128;
-  auto kern = decode_dq_kernel<HD, KMODE, VMODE, SPLIT, HPBL>;
+  auto kern = decode_dq_kernel<HD, KMODE, VMODE, SPLIT, HPBL, ROUTED>;
   static std::atomic<uint64_t> configured{0};  // bit d: attribute set on device d
   int dev = 0;
   cudaGetDevice(&dev);
@@ -1389,7 +1452,9 @@ int launch_dq_hpb(const DecodeArgs& a, const DqParams& dp, cudaStream_t st) {
 template <int HD, int KMODE, int VMODE, bool SPLIT>
 int launch_dq_inst(const DecodeArgs& a, const DqParams& dp, cudaStream_t st) {
   switch (dp.hpb_log2) {
-    case 0: return launch_dq_hpb<HD, KMODE, VMODE, SPLIT, 0>(a, dp, st);
+    case 0:
+      return dp.vheads > 0 ? launch_dq_hpb<HD, KMODE, VMODE, SPLIT, 0, true>(a, dp, st)
+                           : launch_dq_hpb<HD, KMODE, VMODE, SPLIT, 0>(a, dp, st);
     case 1: return launch_dq_hpb<HD, KMODE, VMODE, SPLIT, 1>(a, dp, st);
     default: return launch_dq_hpb<HD, KMODE, VMODE, SPLIT, 2>(a, dp, st);
   }

@@ -30,6 +30,13 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int sr
                "r"(src_bytes)
                : "memory");
 }
+template <int BYTES>  // 4- or 8-byte piece, zero-filled beyond src_bytes
+__device__ __forceinline__ void cp_async_small(uint32_t dst, const void* src, int src_bytes) {
+  static_assert(BYTES == 4 || BYTES == 8, "cp.async piece sizes below 16 are 4 and 8");
+  asm volatile("cp.async.ca.shared.global [%0], [%1], %2, %3;\n" ::"r"(dst), "l"(src), "n"(BYTES),
+               "r"(src_bytes)
+               : "memory");
+}
 template <int OFF>  // destination = dst + OFF, the offset folded into the address operand
 __device__ __forceinline__ void cp_async16_full_at(uint32_t dst, const void* src) {
   asm volatile("cp.async." KNLP_CP_MODE ".shared.global [%0+%2], [%1], 16;\n" ::"r"(dst), "l"(src),

@@ -310,8 +310,71 @@ def gen_contig_cases(out):
     print("contiguous symmetric case done", flush=True)
 
 
+def gen_routed_cases(m, out):
+    """Routed decode (routing/fused_routed_attention.py): the reference's own torch
+    implementation ``reference_routed_decode`` (:496-548) over the DEQUANTIZED contents of a
+    packed cache that the reference's write kernel filled; the dequantization is the
+    reference's ``_cpu_dequant_slot`` (:150-195), slot by slot."""
+    spec = importlib.util.spec_from_file_location(
+        "knlp_ref_routed", os.path.join(REF, "routing", "fused_routed_attention.py"))
+    r = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(r)
+    cases = (
+        # name, dtype, Hq, Hkv, d, block size, blocks in the cache, batch, max selected
+        ("gqa4_d128_p16", "bf16", 8, 2, 128, 16, 24, 2, 9),
+        ("gqa2_d64_p32", "f16", 4, 2, 64, 32, 10, 3, 4),
+        ("mha_d128_p64", "f16", 2, 2, 128, 64, 6, 1, 5),
+    )
+    for name, dtype, hq, hkv, d, P, nb, B, max_sel in cases:
+        g = torch.Generator().manual_seed(4100 + d + P)
+        kvdt = DT[dtype]
+        k, v = make_kv(g, nb * P, hkv, d, kvdt, special_rows=False)
+        slots = torch.arange(nb * P, dtype=torch.int64)
+        q = torch.randn(B, hq, d, generator=g).to(kvdt)
+        tables = torch.zeros(B, hkv, max_sel, dtype=torch.int32)
+        counts = torch.zeros(B, hkv, dtype=torch.int32)
+        for b in range(B):
+            for h in range(hkv):
+                n = int(torch.randint(1, max_sel + 1, (1,), generator=g))
+                counts[b, h] = n
+                tables[b, h, :n] = torch.randperm(nb, generator=g)[:n].to(torch.int32)
+        counts[0, 0] = max_sel
+        tables[0, 0] = torch.randperm(nb, generator=g)[:max_sel].to(torch.int32)
+        if B > 1:
+            counts[1, hkv - 1] = 0  # a head with nothing selected: zeros
+        rec = dict(query=q.float().numpy(), block_tables=tables.numpy(), block_counts=counts.numpy(), q_dtype=dtype,
+                   block_size=P, num_blocks=nb, num_kv_heads=hkv, head_size=d)
+        for mode, asym in (("asym", True), ("sym", False)):
+            kc, vc, ks, vs, kz, vz = alloc_cache(nb, P, hkv, d)
+            m.reshape_and_cache_int4(k, v, kc, vc, ks, vs, slots, kz if asym else None,
+                                     vz if asym else None, asymmetric=asym)
+            kd = torch.zeros(nb, P, hkv, d)
+            vd = torch.zeros(nb, P, hkv, d)
+            for blk in range(nb):
+                for off in range(P):
+                    for h in range(hkv):
+                        kd[blk, off, h] = torch.tensor(m._cpu_dequant_slot(
+                            kc, ks, blk, off, h, d, n_values=d, zeros=kz if asym else None))
+                        vd[blk, off, h] = torch.tensor(m._cpu_dequant_slot(
+                            vc, vs, blk, off, h, d, n_values=d, zeros=vz if asym else None))
+            o = r.reference_routed_decode(q.float(), kd, vd, tables.long(), counts)
+            rec[f"{mode}_out"] = o.float().numpy()
+            rec[f"{mode}_k_cache"], rec[f"{mode}_v_cache"] = kc.numpy(), vc.numpy()
+            rec[f"{mode}_k_scales"], rec[f"{mode}_v_scales"] = f16_bits(ks), f16_bits(vs)
+            if asym:
+                rec["asym_k_zeros"], rec["asym_v_zeros"] = f16_bits(kz), f16_bits(vz)
+        out[f"routed_{name}"] = rec
+        print("routed", name, "done", flush=True)
+
+
 def main():
     out = {}
+    if "--only-routed" in sys.argv:
+        gen_routed_cases(load_reference(), out)
+        for name, rec in out.items():
+            np.savez_compressed(os.path.join(HERE, name + ".npz"), **rec)
+            print("saved", name)
+        return
     if "--only-contig" in sys.argv:
         gen_contig_cases(out)
         for name, rec in out.items():
