@@ -116,6 +116,85 @@ __device__ __forceinline__ void load_q_groups(const void* base, int64_t row, int
   }
 }
 
+// Second half of merge_pair: a thread owns ITEMS (row, four elements) items and keeps
+// their sums; the partial outputs are fetched kBatch parts of every item at a time, all
+// those loads independent of each other (about 20 vector loads in flight per thread: the
+// partials sit in L2, and a dependent round of loads costs over a microsecond while the
+// rest of the machine streams).
+template <int HD, int ITEMS>
+__device__ __forceinline__ void merge_rows(const float* pm, const float* pl, const float* po,
+                                           const int parts, const int heads, float* sw,
+                                           const int tile, const bool one_pass,
+                                           const float* s_mrow, const float* s_irow, void* out,
+                                           const int out_dtype, const int64_t out_row_stride,
+                                           const int64_t row0, const int emit_partial) {
+  const int tid = threadIdx.x;
+  constexpr int kVec = HD / 4;
+  constexpr int kBatch = ITEMS >= 10 ? 2 : 20 / ITEMS;
+  const float4* po4 = reinterpret_cast<const float4*>(po);
+  float4 acc[ITEMS];
+#pragma unroll
+  for (int k = 0; k < ITEMS; ++k) acc[k] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  for (int p0 = 0; p0 < parts; p0 += tile) {
+    const int np = min(tile, parts - p0);
+    if (!one_pass) {
+      __syncthreads();  // the previous tile's weights are no longer read
+      for (int i = tid; i < heads * np; i += kThreads) {
+        const int r = i / np, p = p0 + i % np;
+        const float l1 = __ldcg(pl + p * heads + r);
+        sw[r * tile + (p - p0)] =
+            l1 > 0.0f ? __expf(__ldcg(pm + p * heads + r) - s_mrow[r]) * s_irow[r] : 0.0f;
+      }
+      __syncthreads();
+    }
+    for (int pb = 0; pb < np; pb += kBatch) {
+      float4 v[ITEMS][kBatch];
+#pragma unroll
+      for (int k = 0; k < ITEMS; ++k) {
+        const int i = tid + k * kThreads;
+        const int r = i / kVec, e4 = i % kVec;
+#pragma unroll
+        for (int q = 0; q < kBatch; ++q) {
+          // a member that saw no token wrote zeros, so no value needs skipping
+          const bool valid = i < heads * kVec && pb + q < np;
+          v[k][q] = valid ? __ldcg(po4 + (static_cast<int64_t>(p0 + pb + q) * heads + r) * kVec + e4)
+                          : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < ITEMS; ++k) {
+        const int i = tid + k * kThreads;
+        const int r = min(i / kVec, heads - 1);
+#pragma unroll
+        for (int q = 0; q < kBatch; ++q) {
+          const float wgt = pb + q < np ? sw[r * tile + pb + q] : 0.0f;
+          acc[k].x = fmaf(v[k][q].x, wgt, acc[k].x);
+          acc[k].y = fmaf(v[k][q].y, wgt, acc[k].y);
+          acc[k].z = fmaf(v[k][q].z, wgt, acc[k].z);
+          acc[k].w = fmaf(v[k][q].w, wgt, acc[k].w);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < ITEMS; ++k) {
+    const int i = tid + k * kThreads;
+    if (i < heads * kVec) {
+      const int r = i / kVec, e4 = i % kVec;
+      const int64_t o = (row0 + r) * out_row_stride + 4 * e4;
+      if (emit_partial) {
+        float* orow = static_cast<float*>(out) + o;
+        orow[0] = acc[k].x; orow[1] = acc[k].y; orow[2] = acc[k].z; orow[3] = acc[k].w;
+      } else {
+        store_elem_rt(out, o, acc[k].x, out_dtype);
+        store_elem_rt(out, o + 1, acc[k].y, out_dtype);
+        store_elem_rt(out, o + 2, acc[k].z, out_dtype);
+        store_elem_rt(out, o + 3, acc[k].w, out_dtype);
+      }
+    }
+  }
+}
+
 // Merge of the partials of one pair by the CTA that arrived last: out[row] = sum_p w_p o_p
 // with w_p = l_p e^(m_p - m) / sum_q l_q e^(m_q - m).  pm, pl: [parts][heads]; po: [parts]
 // [heads][HD]; sw: shared-memory scratch of sw_floats floats; s_mrow, s_irow: MAXH floats
@@ -177,73 +256,22 @@ __device__ __noinline__ void merge_pair(const float* pm, const float* pl, const 
     }
   }
   __syncthreads();
-  // (2) out[row] = sum_p w_p o_p.  A thread owns up to kItems (row, four elements) items
-  // and keeps their sums; the partial outputs are fetched kBatch parts of every item at
-  // a time, all those loads independent of each other.
-  constexpr int kVec = HD / 4;
-  constexpr int kItems = (MAXH * kVec + kThreads - 1) / kThreads;
-  constexpr int kBatch = kItems >= 16 ? 1 : 16 / kItems;
-  const float4* po4 = reinterpret_cast<const float4*>(po);
-  float4 acc[kItems];
-#pragma unroll
-  for (int k = 0; k < kItems; ++k) acc[k] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-  for (int p0 = 0; p0 < parts; p0 += tile) {
-    const int np = min(tile, parts - p0);
-    if (!one_pass) {
-      __syncthreads();  // the previous tile's weights are no longer read
-      for (int i = tid; i < heads * np; i += kThreads) {
-        const int r = i / np, p = p0 + i % np;
-        const float l1 = __ldcg(pl + p * heads + r);
-        sw[r * tile + (p - p0)] =
-            l1 > 0.0f ? __expf(__ldcg(pm + p * heads + r) - s_mrow[r]) * s_irow[r] : 0.0f;
-      }
-      __syncthreads();
-    }
-    for (int pb = 0; pb < np; pb += kBatch) {
-      float4 v[kItems][kBatch];
-#pragma unroll
-      for (int k = 0; k < kItems; ++k) {
-        const int i = tid + k * kThreads;
-        const int r = i / kVec, e4 = i % kVec;
-#pragma unroll
-        for (int q = 0; q < kBatch; ++q) {
-          // a member that saw no token wrote zeros, so no value needs skipping
-          const bool valid = i < heads * kVec && pb + q < np;
-          v[k][q] = valid ? __ldcg(po4 + (static_cast<int64_t>(p0 + pb + q) * heads + r) * kVec + e4)
-                          : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        }
-      }
-#pragma unroll
-      for (int k = 0; k < kItems; ++k) {
-        const int i = tid + k * kThreads;
-        const int r = min(i / kVec, heads - 1);
-#pragma unroll
-        for (int q = 0; q < kBatch; ++q) {
-          const float wgt = pb + q < np ? sw[r * tile + pb + q] : 0.0f;
-          acc[k].x = fmaf(v[k][q].x, wgt, acc[k].x);
-          acc[k].y = fmaf(v[k][q].y, wgt, acc[k].y);
-          acc[k].z = fmaf(v[k][q].z, wgt, acc[k].z);
-          acc[k].w = fmaf(v[k][q].w, wgt, acc[k].w);
-        }
-      }
-    }
-  }
-#pragma unroll
-  for (int k = 0; k < kItems; ++k) {
-    const int i = tid + k * kThreads;
-    if (i < heads * kVec) {
-      const int r = i / kVec, e4 = i % kVec;
-      const int64_t o = (row0 + r) * out_row_stride + 4 * e4;
-      if (emit_partial) {
-        float* orow = static_cast<float*>(out) + o;
-        orow[0] = acc[k].x; orow[1] = acc[k].y; orow[2] = acc[k].z; orow[3] = acc[k].w;
-      } else {
-        store_elem_rt(out, o, acc[k].x, out_dtype);
-        store_elem_rt(out, o + 1, acc[k].y, out_dtype);
-        store_elem_rt(out, o + 2, acc[k].z, out_dtype);
-        store_elem_rt(out, o + 3, acc[k].w, out_dtype);
-      }
-    }
+  // (2) out[row] = sum_p w_p o_p, with as many (row, four elements) items per thread as
+  // the pair really has heads: the fewer items, the more parts are fetched at once.
+  const int items = (heads * (HD / 4) + kThreads - 1) / kThreads;
+  if (items <= 1) {
+    merge_rows<HD, 1>(pm, pl, po, parts, heads, sw, tile, one_pass, s_mrow, s_irow, out,
+                      out_dtype, out_row_stride, row0, emit_partial);
+  } else if (items <= 2) {
+    merge_rows<HD, 2>(pm, pl, po, parts, heads, sw, tile, one_pass, s_mrow, s_irow, out,
+                      out_dtype, out_row_stride, row0, emit_partial);
+  } else if (items <= 4 || MAXH * (HD / 4) <= 4 * kThreads) {
+    merge_rows<HD, 4>(pm, pl, po, parts, heads, sw, tile, one_pass, s_mrow, s_irow, out,
+                      out_dtype, out_row_stride, row0, emit_partial);
+  } else {
+    merge_rows<HD, (MAXH * (HD / 4) + kThreads - 1) / kThreads>(
+        pm, pl, po, parts, heads, sw, tile, one_pass, s_mrow, s_irow, out, out_dtype,
+        out_row_stride, row0, emit_partial);
   }
 }
 
@@ -1360,10 +1388,14 @@ decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
     if (tid == 0) {
       const int old = atomicAdd(arrive, 1);
       const int last = (old == parts - 1) ? 1 : 0;
-      if (last) {  // every member has taken its last ticket: ready for the next launch
-        *arrive = 0;
-        *ticket = 0;
-        if (!dp.fuse) {
+      if (last) {
+        // the other members' partials are read after this point (the CTA's loads come
+        // after the barrier below); nothing of this thread is in flight, so the fence is
+        // cheap here - after the counter resets it would wait for their round trip
+        __threadfence();
+        if (!dp.fuse) {  // every member has taken its last ticket: ready for the next launch
+          *arrive = 0;
+          *ticket = 0;
           dp.pair_info[2 * pair] = first_slot;
           dp.pair_info[2 * pair + 1] = parts;
         }
@@ -1372,7 +1404,10 @@ decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
     }
     __syncthreads();
     if (!dp.fuse || !s_last) return;
-    __threadfence();
+    if (tid == 0) {  // ready for the next launch; off the merge's critical path
+      *arrive = 0;
+      *ticket = 0;
+    }
     merge_pair<HD, HPB * 8>(dp.ws_m + static_cast<int64_t>(first_slot) * heads,
                             dp.ws_l + static_cast<int64_t>(first_slot) * heads,
                             dp.ws_o + static_cast<int64_t>(first_slot) * heads * HD, parts, heads,
