@@ -14,6 +14,12 @@ KNLP_DECL_PAIR(KNLP_KV_INT4_SYM, KNLP_KV_INT4_SYM);
 KNLP_DECL_PAIR(KNLP_KV_INT8_G32, KNLP_KV_INT4_ASYM);
 KNLP_DECL_PAIR(KNLP_KV_INT8_G32, KNLP_KV_INT4_SYM);
 KNLP_DECL_PAIR(KNLP_KV_INT8_G32, KNLP_KV_INT8_G32);
+KNLP_DECL_PAIR(KNLP_KV_F16, KNLP_KV_INT4_ASYM);
+KNLP_DECL_PAIR(KNLP_KV_F16, KNLP_KV_INT4_SYM);
+KNLP_DECL_PAIR(KNLP_KV_F16, KNLP_KV_INT8_G32);
+KNLP_DECL_PAIR(KNLP_KV_BF16, KNLP_KV_INT4_ASYM);
+KNLP_DECL_PAIR(KNLP_KV_BF16, KNLP_KV_INT4_SYM);
+KNLP_DECL_PAIR(KNLP_KV_BF16, KNLP_KV_INT8_G32);
 #undef KNLP_DECL_PAIR
 
 namespace {
@@ -37,6 +43,17 @@ int with_pair(int km, int vm, F&& f) {
   if (km == KNLP_KV_INT8_G32 && vm == KNLP_KV_INT8_G32)
     return f(std::integral_constant<int, KNLP_KV_INT8_G32>{},
              std::integral_constant<int, KNLP_KV_INT8_G32>{});
+  // an unquantized K plane (fp16 or bf16) against each V mode
+  if (km == KNLP_KV_F16 || km == KNLP_KV_BF16) {
+    auto with_v = [&](auto k) -> int {
+      if (vm == KNLP_KV_INT4_ASYM) return f(k, std::integral_constant<int, KNLP_KV_INT4_ASYM>{});
+      if (vm == KNLP_KV_INT4_SYM) return f(k, std::integral_constant<int, KNLP_KV_INT4_SYM>{});
+      if (vm == KNLP_KV_INT8_G32) return f(k, std::integral_constant<int, KNLP_KV_INT8_G32>{});
+      return -1000;
+    };
+    return km == KNLP_KV_F16 ? with_v(std::integral_constant<int, KNLP_KV_F16>{})
+                             : with_v(std::integral_constant<int, KNLP_KV_BF16>{});
+  }
   return -1000;  // no tensor-core instantiation for this pair
 }
 
@@ -128,6 +145,9 @@ int launch_decode_dq(const DecodeArgs& a_in, float* ws, int64_t ws_floats, int* 
     dp.clip_ratio = nt->clip_ratio;
   }
   const bool split = n_rep <= 4;
+  // bf16 K with one column per head: q enters the product as a single bf16, which is exact
+  // only for bf16 queries
+  if (a.k.mode == KNLP_KV_BF16 && !split && a.q_dtype != KNLP_BF16) return 1;
   const int rc = with_pair(a.k.mode, a.v.mode, [&](auto k, auto v) {
     return launch_dq_pair<decltype(k)::value, decltype(v)::value>(a, dp, split, st);
   });

@@ -116,6 +116,45 @@ __device__ __forceinline__ void load_q_groups(const void* base, int64_t row, int
   }
 }
 
+// The same for an unquantized K plane, whose tile is the A operand as it lies in memory:
+// slot (2i, 2i + 1) of group g is the element pair 32g + 8i + 2*quad (+1), i = 0..3 - the
+// B fragment rows of the two 16-wide steps of the group.
+template <int NG>
+__device__ __forceinline__ void load_q_pairs(const void* base, int64_t row, int quad, int dt,
+                                             float out[NG][8]) {
+  if (dt == KNLP_F32) {
+    const float* p = static_cast<const float*>(base) + row + 2 * quad;
+    float2 v[NG][4];
+#pragma unroll
+    for (int g = 0; g < NG; ++g)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) v[g][i] = __ldg(reinterpret_cast<const float2*>(p + 32 * g + 8 * i));
+#pragma unroll
+    for (int g = 0; g < NG; ++g)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        out[g][2 * i] = v[g][i].x;
+        out[g][2 * i + 1] = v[g][i].y;
+      }
+    return;
+  }
+  const uint16_t* p = static_cast<const uint16_t*>(base) + row + 2 * quad;
+  uint32_t w[NG][4];
+#pragma unroll
+  for (int g = 0; g < NG; ++g)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) w[g][i] = __ldg(reinterpret_cast<const uint32_t*>(p + 32 * g + 8 * i));
+  const bool f16 = dt == KNLP_F16;
+#pragma unroll
+  for (int g = 0; g < NG; ++g)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[g][i]));
+      out[g][2 * i] = f16 ? f.x : __uint_as_float(w[g][i] << 16);
+      out[g][2 * i + 1] = f16 ? f.y : __uint_as_float(w[g][i] & 0xFFFF0000u);
+    }
+}
+
 // Second half of merge_pair: a thread owns ITEMS (row, four elements) items and keeps
 // their sums; the partial outputs are fetched kBatch parts of every item at a time, all
 // those loads independent of each other (about 20 vector loads in flight per thread: the
@@ -381,8 +420,17 @@ __device__ __noinline__ void append_token(const void* ksrc, const void* vsrc, co
   }
 }
 
+// CTAs per SM the register budget is set for: as many as the stages leave room for in
+// shared memory (an unquantized K plane: three; the packed planes: kCtasPerSm).
+template <int HD, int KMODE, int VMODE>
+constexpr int dq_ctas_per_sm() {
+  using G = Geo<HD, KMODE, VMODE, kTilePad>;
+  constexpr int fit = 232448 / (G::kSmemBytes + 2048);
+  return fit < 1 ? 1 : fit < kCtasPerSm ? fit : kCtasPerSm;
+}
+
 template <int HD, int KMODE, int VMODE, bool SPLIT, int HPBL, bool ROUTED = false>
-__global__ void __launch_bounds__(kThreads, kCtasPerSm)
+__global__ void __launch_bounds__(kThreads, dq_ctas_per_sm<HD, KMODE, VMODE>())
 decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
   static_assert(!ROUTED || HPBL == 0, "per-kv-head page tables: one kv head per CTA");
   using G = Geo<HD, KMODE, VMODE, kTilePad>;
@@ -390,6 +438,8 @@ decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
   constexpr bool kInt8V = G::kInt8V;
   constexpr int NG = G::NG;
   constexpr bool kInt8K = G::kInt8K;
+  constexpr bool kFpK = G::kFpK;  // unquantized K: no scale rows, the tile IS the A operand
+  constexpr bool kBf16K = (KMODE == KNLP_KV_BF16);
   constexpr bool kAsymK = (KMODE == KNLP_KV_INT4_ASYM);
   constexpr bool kAsymV = (VMODE == KNLP_KV_INT4_ASYM);
   constexpr int hpb_log2 = HPBL;
@@ -520,7 +570,7 @@ decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
   // copy role: the 16-byte pieces of a stage are dealt to the threads in memory order
   // (token, head, piece); a thread owns pieces tid, tid + 128, ... of each plane
   constexpr int kKPer = G::KCH / 2, kVPer = G::VCH / 2;
-  constexpr int kKChLog = G::KCH == 8 ? 3 : G::KCH == 4 ? 2 : 1;
+  constexpr int kKChLog = G::KCH == 16 ? 4 : G::KCH == 8 ? 3 : G::KCH == 4 ? 2 : 1;
   constexpr int kVChLog = G::VCH == 8 ? 3 : G::VCH == 4 ? 2 : 1;
   constexpr int k_lg = hpb_log2 + kKChLog, v_lg = hpb_log2 + kVChLog;
   const int k_tt0 = tid >> k_lg, v_tt0 = tid >> v_lg;
@@ -548,7 +598,8 @@ decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
   const int s_byte = (tid % kSPieces) * 16;
   constexpr int s_tb = G::SB << hpb_log2;
   const int s_tt = s_byte / s_tb;
-  const bool s_on = s_arr < 4 && !((s_arr == 1 && !kAsymK) || (s_arr == 3 && !kAsymV));
+  const bool s_on = s_arr < 4 && !((s_arr == 0 && kFpK) || (s_arr == 1 && !kAsymK) ||
+                                   (s_arr == 3 && !kAsymV));
   const Plane& s_pl = (s_arr >= 2) ? a.v : a.k;
   const bool s_zero = (s_arr & 1) != 0;
   const __half* s_base = s_zero ? s_pl.zeros : s_pl.scales;
@@ -572,7 +623,7 @@ decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
   const int lm_q = lane >> 4;
   const uint32_t k_lm0 = smem_base + G::kOffK + warp * G::kTileK + lm_row * G::KB;
   const uint32_t v_lm0 = smem_base + G::kOffV + warp * G::kTileV + lm_row * G::VB;
-  constexpr int kKLoads = kInt8K ? NG : NG / 2;
+  constexpr int kKLoads = kFpK ? 2 * NG : kInt8K ? NG : NG / 2;
   constexpr int kVLoads = kInt8V ? NG : NG / 2;
   uint32_t k_lm[kKLoads], v_lm[kVLoads];
 #pragma unroll
@@ -620,7 +671,7 @@ decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
     }
 
     // the pair's last member also appends the step's new token
-    const bool has_new = appending && slot - first_slot == parts - 1;
+    const bool has_new = !kFpK && appending && slot - first_slot == parts - 1;
     bool have_work = true;
     if (!home && !has_new) {  // one thread looks, so that the whole CTA goes the same way
       if (tid == 0) s_flag = dyn0 + *reinterpret_cast<volatile int*>(ticket) < n_chunks ? 1 : 0;
@@ -671,7 +722,7 @@ decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
 #pragma unroll
         for (int n = 0; n < 2; ++n) {
           const int arr = (tid >> 6) + 2 * n;
-          if ((arr == 1 && !kAsymK) || (arr == 3 && !kAsymV)) continue;
+          if ((arr == 0 && kFpK) || (arr == 1 && !kAsymK) || (arr == 3 && !kAsymV)) continue;
           const Plane& pl = n ? a.v : a.k;
           const __half* base = (arr & 1) ? pl.zeros : pl.scales;
           const int64_t* st = (arr & 1) ? pl.zs : pl.ss;
@@ -844,6 +895,7 @@ decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
     // ---------------- the step's new token (the pair's last member): while the first
     // copies are in flight, one warp per kv head quantizes it, stores it and leaves its
     // scores and value row in shared memory for the epilogue ----------------
+    if constexpr (!kFpK)  // (an unquantized K plane takes no fused append)
     if (has_new && w_tile == 0) {
       const int kvh_e = hb * HPB + w_head;
       int blk = __ldg(bt_row + (len >> dp.page_log2));
@@ -881,7 +933,11 @@ decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
       float xq[NG][8];
       // slot e of group g is element 32g + 8ft + e (INT4 K) or 32g + 16(e>>2) + 4ft + (e&3)
       if (live) {
-        load_q_groups<NG, kInt8K>(a.q, qbase, ft, a.q_dtype, xq);
+        if constexpr (kFpK) {
+          load_q_pairs<NG>(a.q, qbase, ft, a.q_dtype, xq);
+        } else {
+          load_q_groups<NG, kInt8K>(a.q, qbase, ft, a.q_dtype, xq);
+        }
       } else {
 #pragma unroll
         for (int g = 0; g < NG; ++g)
@@ -891,13 +947,30 @@ decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
       float colsum[NG];
 #pragma unroll
       for (int g = 0; g < NG; ++g) {
+        if constexpr (kBf16K) {
+          // bf16 parts of q: hi = bf16(q), lo = bf16(q - hi)
+          uint32_t u[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float x = xq[g][e];
+            __nv_bfloat16 b = __float2bfloat16_rn(x);
+            if (lo_part) b = __float2bfloat16_rn(x - __bfloat162float(b));
+            u[e] = *reinterpret_cast<const uint16_t*>(&b);
+          }
+          colsum[g] = 0.0f;
+          bq[g][0][0] = u[0] | (u[1] << 16);
+          bq[g][0][1] = u[2] | (u[3] << 16);
+          bq[g][1][0] = u[4] | (u[5] << 16);
+          bq[g][1][1] = u[6] | (u[7] << 16);
+          continue;
+        }
         __half v[8];
         float s = 0.0f;
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           float x = xq[g][e];
           float wgt = 1.0f;
-          if constexpr (!kInt8K) {
+          if constexpr (!kInt8K && !kFpK) {
             // the A operand holds, per byte, the even nibble alone and the whole byte (even
             // + 16 * odd): the even slot takes q_e - q_o / 16, the odd slot q_o / 16 (with q
             // as a single fp16 the nibbles are isolated and only the odd slot is scaled)
@@ -914,7 +987,7 @@ decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
           v[e] = h;
         }
         colsum[g] = s;
-        if constexpr (kInt8K) {
+        if constexpr (kInt8K || kFpK) {
           bq[g][0][0] = pack_h2(v[0], v[1]);
           bq[g][0][1] = pack_h2(v[2], v[3]);
           bq[g][1][0] = pack_h2(v[4], v[5]);
@@ -1004,7 +1077,20 @@ decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
       for (int g = 0; g < NG; ++g)
 #pragma unroll
         for (int i = 0; i < 4; ++i) sacc[g][i] = 0.0f;
-      if constexpr (kInt8K) {
+      if constexpr (kFpK) {
+        // the tile as it lies in memory is the A operand: one ldmatrix and one MMA per 16
+        // elements of the head dimension, all into one accumulator (no per-group scale)
+#pragma unroll
+        for (int i = 0; i < 2 * NG; ++i) {
+          uint32_t w[4];
+          ldmatrix_x4_at<stage_off>(k_lm[i], w);
+          if constexpr (kBf16K) {
+            mma16816_bf16(sacc[0], w[0], w[1], w[2], w[3], bq[i >> 1][i & 1][0], bq[i >> 1][i & 1][1]);
+          } else {
+            mma16816(sacc[0], w[0], w[1], w[2], w[3], bq[i >> 1][i & 1][0], bq[i >> 1][i & 1][1]);
+          }
+        }
+      } else if constexpr (kInt8K) {
 #pragma unroll
         for (int g = 0; g < NG; ++g) {
           uint32_t w[4];
@@ -1042,8 +1128,21 @@ decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
       // ---------------- fold scales / zeros, mask, online softmax ----------------
       float sc[2][NH];
       {
+        if constexpr (kFpK) {
+          constexpr float kMulFp = 1.4426950408889634f;  // scores in the log2 domain
+          const float mul = rsqrtf(static_cast<float>(HD)) * kMulFp;
 #pragma unroll
-        for (int rh = 0; rh < 2; ++rh) {
+          for (int rh = 0; rh < 2; ++rh) {
+            if constexpr (SPLIT) {
+              sc[rh][0] = (sacc[0][2 * rh] + sacc[0][2 * rh + 1]) * mul;
+            } else {
+              sc[rh][0] = sacc[0][2 * rh] * mul;
+              sc[rh][NH - 1] = sacc[0][2 * rh + 1] * mul;
+            }
+          }
+        }
+#pragma unroll
+        for (int rh = 0; rh < (kFpK ? 0 : 2); ++rh) {
           float ks[NG], kz[NG];
           const __half2* sp2 =
               reinterpret_cast<const __half2*>(st + G::kOffKs + sc_row0 + rh * sc_row8);

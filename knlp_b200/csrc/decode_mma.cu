@@ -278,6 +278,7 @@ bool plane_ok(const Plane& p, int head_dim, int row_bytes, int hpb, int n_kv_hea
   for (int i = 0; i < 2; ++i)
     if (p.cs[i] % 16 || p.cs[i] < 0 || p.cs[i] > kMax) return false;
   const int ng = head_dim / 32;
+  if (p.mode == KNLP_KV_F16 || p.mode == KNLP_KV_BF16) return true;  // no scale rows
   if (!scale_array_ok(p.scales, p.ss, ng, hpb, n_kv_heads)) return false;
   if (p.zeros && !scale_array_ok(p.zeros, p.zs, ng, hpb, n_kv_heads)) return false;
   return true;
@@ -297,7 +298,9 @@ int decode_mma_layout(const DecodeArgs& a, int* hpb_log2_out, int* page_log2_out
   int hpb_log2 = kWarpsLog;
   while (hpb_log2 > 0 && (a.n_kv_heads % (1 << hpb_log2))) --hpb_log2;
   const int hpb = 1 << hpb_log2;
-  const int kb = a.k.mode == KNLP_KV_INT8_G32 ? a.head_dim : a.head_dim / 2;
+  const int kb = (a.k.mode == KNLP_KV_F16 || a.k.mode == KNLP_KV_BF16) ? 2 * a.head_dim
+                 : a.k.mode == KNLP_KV_INT8_G32                           ? a.head_dim
+                                                                          : a.head_dim / 2;
   if (!plane_ok(a.k, a.head_dim, kb, hpb, a.n_kv_heads) ||
       !plane_ok(a.v, a.head_dim, a.v.mode == KNLP_KV_INT8_G32 ? a.head_dim : a.head_dim / 2, hpb,
                 a.n_kv_heads))

@@ -79,6 +79,15 @@ __device__ __forceinline__ void mma16816(float c[4], uint32_t a0, uint32_t a1, u
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+// the same with bf16 inputs (an unquantized bf16 K plane against q split into bf16 parts)
+__device__ __forceinline__ void mma16816_bf16(float c[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                              uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
@@ -228,8 +237,10 @@ template <int HD, int KMODE, int VMODE, int PAD>
 struct Geo {
   static constexpr bool kInt8K = (KMODE == KNLP_KV_INT8_G32);
   static constexpr bool kInt8V = (VMODE == KNLP_KV_INT8_G32);
+  // an unquantized fp16 / bf16 K plane: rows of 2 * HD bytes, no scale or zero rows
+  static constexpr bool kFpK = (KMODE == KNLP_KV_F16 || KMODE == KNLP_KV_BF16);
   static constexpr int NG = HD / 32;
-  static constexpr int KB = kInt8K ? HD : HD / 2;  // K row bytes
+  static constexpr int KB = kFpK ? 2 * HD : kInt8K ? HD : HD / 2;  // K row bytes
   static constexpr int VB = kInt8V ? HD : HD / 2;  // V row bytes
   static constexpr int KCH = KB / 16;              // 16-byte pieces per K row
   static constexpr int VCH = VB / 16;
@@ -239,8 +250,8 @@ struct Geo {
   static constexpr int kOffK = 0;
   static constexpr int kOffV = kOffK + kWarpsCta * kTileK;
   static constexpr int kOffKs = kOffV + kWarpsCta * kTileV;
-  static constexpr int kOffKz = kOffKs + kRows * SB;
-  static constexpr int kOffVs = kOffKz + kRows * SB;
+  static constexpr int kOffKz = kOffKs + (kFpK ? 0 : kRows * SB);
+  static constexpr int kOffVs = kOffKz + (kFpK ? 0 : kRows * SB);
   static constexpr int kOffVz = kOffVs + kRows * SB;
   static constexpr int kStageBytes = kOffVz + kRows * SB;
   // Four stages, or three where four would no longer let kCtasPerSm CTAs share the
@@ -253,7 +264,11 @@ struct Geo {
 // xor swizzle of the 16-byte column index of row r (0..15) for rows of CH pieces
 template <int CH>
 __device__ __forceinline__ int swz(int r) {
-  return (r / (8 / CH)) & (CH - 1);
+  if constexpr (CH >= 8) {
+    return r & 7;  // rows of 128 bytes or more: the eight rows of an 8x8 matrix differ
+  } else {
+    return (r / (8 / CH)) & (CH - 1);
+  }
 }
 
 // Extra launch parameters computed on the host.

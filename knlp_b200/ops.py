@@ -611,8 +611,10 @@ def kfp16_vint4_decode(
     max_seq_len: Optional[int] = None,
     n_splits: Optional[int] = None,
 ) -> torch.Tensor:
-    """K unquantized / V INT4 hybrid decode (reference :1159-1224).  Runs on the
-    stride-generic kernel (correct, not tuned)."""
+    """K unquantized / V INT4 hybrid decode (reference :1159-1224).  The balanced
+    tensor-core launch takes it (the fp16 / bf16 K tile is the MMA operand as it lies in
+    memory); a given ``n_splits`` or a layout it cannot address runs the stride-generic
+    kernel."""
     _need_cuda(key_cache_fp16, value_cache_int4, v_scales, v_zeros)
     kp = _fp_plane(key_cache_fp16)
     vp = _plane(value_cache_int4, v_scales, v_zeros if asymmetric else None,
@@ -637,7 +639,8 @@ def kfp16_vint8_decode(
     max_seq_len: Optional[int] = None,
     n_splits: Optional[int] = None,
 ) -> torch.Tensor:
-    """K unquantized / V INT8 hybrid decode (reference :1975-2028).  Stride-generic kernel."""
+    """K unquantized / V INT8 hybrid decode (reference :1975-2028).  Kernels as for
+    ``kfp16_vint4_decode``."""
     _need_cuda(key_cache_fp16, value_cache_int8, v_scales)
     kp = _fp_plane(key_cache_fp16)
     vp = _plane(value_cache_int8, v_scales, None, _lib.KV_INT8_G32)

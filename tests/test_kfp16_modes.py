@@ -94,3 +94,71 @@ def test_unquantized_plane_is_refused_where_it_has_no_meaning():
                                        64, 16, 1, 16, p, p, p, 0, None) == -4
     with pytest.raises(TypeError):
         ops._fp_plane(torch.zeros(1, 16, 1, 64))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kdt,qdt,hq,hkv,d,v8", [
+    (torch.float16, torch.float16, 32, 8, 128, False),   # GQA-4, four kv heads per CTA
+    (torch.bfloat16, torch.bfloat16, 32, 8, 128, True),  # bf16 product, INT8 V
+    (torch.bfloat16, torch.float32, 8, 2, 128, False),   # q split into two bf16 parts
+    (torch.float16, torch.float32, 6, 6, 64, False),     # MHA, d 64, two kv heads per CTA
+    (torch.float16, torch.bfloat16, 16, 2, 128, True),   # GQA-8: one column per q head
+    (torch.bfloat16, torch.bfloat16, 8, 1, 128, False),  # GQA-8 with bf16 (exact for bf16 q)
+    (torch.bfloat16, torch.float16, 8, 1, 128, False),   # GQA-8, bf16 K, fp16 q: generic kernel
+])
+def test_kfp16_tensor_core_path_vs_generic_and_oracle(kdt, qdt, hq, hkv, d, v8, cuda_device):
+    """Ragged lengths over shuffled pages: the balanced tensor-core launch (default) against
+    the stride-generic CUDA-core kernel (a given split count selects it) and the oracle."""
+    from knlp_b200 import ops
+    dev, P = cuda_device, 16
+    g = torch.Generator().manual_seed(hq * 131 + d + int(v8))
+    lens = [700, 33, 1, 1500, 64, 257, 16, 0]
+    S = len(lens)
+    blocks = [(L + P - 1) // P for L in lens]
+    nb = sum(blocks) + 3
+    perm = torch.randperm(nb, generator=g).to(torch.int32)
+    bt = torch.zeros(S, max(blocks), dtype=torch.int32)
+    slots, o = [], 0
+    for s, L in enumerate(lens):
+        bt[s, :blocks[s]] = perm[o:o + blocks[s]]
+        o += blocks[s]
+        slots += [int(bt[s, n // P]) * P + n % P for n in range(L)]
+    slots = torch.tensor(slots, dtype=torch.int64)
+    T = int(slots.numel())
+    k = (torch.randn(T, hkv, d, generator=g) * 1.5).to(kdt)
+    k[:, :, 3] *= 8  # an outlier channel
+    v = torch.randn(T, hkv, d, generator=g).to(kdt)
+    q = torch.randn(S, hq, d, generator=g).to(qdt)
+    kcache = torch.zeros(nb, P, hkv, d, dtype=kdt)
+    kcache.view(nb * P, hkv, d)[slots] = k
+    vcache = torch.zeros(nb, P, hkv, d if v8 else d // 2, dtype=torch.int8 if v8 else torch.uint8,
+                         device=dev)
+    vs = torch.zeros(nb, P, hkv, d // 32, dtype=torch.float16, device=dev)
+    vz = torch.zeros_like(vs)
+    if v8:
+        ops.reshape_and_cache_v_int8(v.to(dev), vcache, vs, slots.to(dev))
+    else:
+        ops.reshape_and_cache_v_only_int4(v.to(dev), vcache, vs, slots.to(dev), vz, asymmetric=True)
+    qd, kd, btd = q.to(dev), kcache.to(dev), bt.to(dev)
+    sl = torch.tensor(lens, dtype=torch.int32, device=dev)
+
+    def run(**kw):
+        if v8:
+            return ops.kfp16_vint8_decode(qd, kd, vcache, vs, btd, sl, hkv, d,
+                                          out_dtype=torch.float32, **kw)
+        return ops.kfp16_vint4_decode(qd, kd, vcache, vs, btd, sl, hkv, d, v_zeros=vz,
+                                      asymmetric=True, out_dtype=torch.float32, **kw)
+
+    fast, generic = run(), run(n_splits=2)
+    kn, qn = kcache.float().numpy(), q.float().numpy()
+    if v8:
+        ref = O.kfp16_vint8_decode(qn, kn, vcache.cpu().numpy(), vs.cpu().numpy(), bt.numpy(),
+                                   np.asarray(lens, np.int32), hkv, d)
+    else:
+        ref = O.kfp16_vint4_decode(qn, kn, vcache.cpu().numpy(), vs.cpu().numpy(), bt.numpy(),
+                                   np.asarray(lens, np.int32), hkv, d,
+                                   v_zeros=vz.cpu().numpy(), asymmetric=True)
+    for name, out in (("tensor-core", fast), ("generic", generic)):
+        err = np.abs(out.cpu().numpy() - ref)
+        assert np.all(err <= ATOL + RTOL * np.abs(ref)), f"{name}: max abs err {err.max():.3e}"
+    assert not fast[-1].any()  # the sequence without tokens
