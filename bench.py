@@ -625,6 +625,13 @@ def run_ours(args):
             secondary.append(row)
             del w3, r3, _
             torch.cuda.empty_cache()
+        side = []
+        if world == 1:
+            # the write path and the decode variants beside the headline (one GPU only)
+            side += measure_write_path(torch, ops, workloads, dev, 10, 3)
+            torch.cuda.empty_cache()
+            side += measure_side_kernels(torch, ops, workloads, dev, Ks, peak_gbs)
+            torch.cuda.empty_cache()
         # whole-job numbers: max time over ranks, bytes summed over ranks
         if world > 1:
             for row in secondary:
@@ -637,6 +644,7 @@ def run_ours(args):
                 row["tb_per_s"] = b.item() / (row["us_per_step"] / 1e6) / 1e12
                 row["frac_per_gpu"] = row["tb_per_s"] * 1e3 / world / peak_gbs
                 row.pop("frac", None)
+        secondary += side
 
     if rank == 0:
         ms_step = total_ms / K
@@ -726,20 +734,18 @@ def run_append_loop(args):
         torch.cuda.empty_cache()
 
 
-def run_write_path(args):
-    """Side measurement, not the headline: the quantize-and-append kernel over a prefill-sized
-    batch (tokens x 8 kv heads x 128, bf16, K and V), algorithmic read + write bytes per
-    CUDA-event second.  One JSON line per quantizer."""
-    import torch
-    from knlp_b200 import ops, workloads
-    dev = torch.device("cuda:0")
-    torch.cuda.set_device(dev)
-    n, h, d, P = int((1 << 20) * args.scale), 8, 128, 16
+def measure_write_path(torch, ops, workloads, dev, steps, warmup, scale=1.0):
+    """The quantize-and-append kernel over a prefill-sized batch (tokens x 8 kv heads x 128,
+    bf16, K and V, scattered slots): algorithmic read + write bytes per CUDA-event second,
+    one row per quantizer."""
+    n, h, d, P = int((1 << 20) * scale), 8, 128, 16
     g = torch.Generator(device=dev).manual_seed(1)
     k = torch.randn(n, h, d, device=dev, generator=g).to(torch.bfloat16)
     v = torch.randn(n, h, d, device=dev, generator=g).to(torch.bfloat16)
     slots = torch.randperm(n, device=dev, generator=g).to(torch.int64)  # scattered pages
     nb = (n + P - 1) // P
+    hbm_gbs, peak_kind = peaks()
+    rows = []
     for mode, out_bytes in (("int4_asym", 160), ("int4_sym", 144), ("int8", 272)):
         kc, vc, ks, vs, kz, vz = workloads.alloc_cache(nb, h, d, mode, mode, dev)
         if mode == "int8":
@@ -751,24 +757,92 @@ def run_write_path(args):
             def step():
                 ops.reshape_and_cache_int4(k, v, kc, vc, ks, vs, slots, kz if asym else None,
                                            vz if asym else None, asymmetric=asym)
-        for _ in range(max(args.warmup, 3)):
+        for _ in range(max(warmup, 3)):
             step()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(args.steps):
+        for _ in range(steps):
             step()
         e1.record()
         torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / args.steps
+        ms = e0.elapsed_time(e1) / steps
         byts = n * h * (2 * d * 2 + out_bytes) + n * 8  # bf16 K and V in, codes/scales out, slots
-        hbm_gbs, peak_kind = peaks()
-        print(json.dumps({"write_path": mode, "tokens": n, "kv_heads": h, "head_dim": d,
-                          "src_dtype": "bf16", "ms_per_step": ms, "algorithmic_bytes": byts,
-                          "value": byts / ms / 1e9, "unit": "TB/s",
-                          "frac_of_hbm_peak": byts / ms / 1e6 / hbm_gbs, "peak": peak_kind,
-                          "note": "inputs 4.3 GB > L2; K and V quantized per step"}))
+        rows.append({"write_path": mode, "tokens": n, "kv_heads": h, "head_dim": d,
+                     "src_dtype": "bf16", "ms_per_step": ms, "algorithmic_bytes": byts,
+                     "value": byts / ms / 1e9, "unit": "TB/s",
+                     "frac_of_hbm_peak": byts / ms / 1e6 / hbm_gbs, "peak": peak_kind,
+                     "note": "inputs 4.3 GB > L2; K and V quantized per step"})
         del kc, vc, ks, vs, kz, vz
+    return rows
+
+
+def measure_side_kernels(torch, ops, workloads, dev, steps, peak_gbs):
+    """Decode variants beside the headline, on the cache of llama8b_b32_8k (32 sequences x
+    8192 tokens x 8 kv heads, shuffled 16-token pages), each one launch captured in a CUDA
+    graph and replayed: an unquantized bf16 K plane with INT4 V, and routed decode (every kv
+    head attends to its own top-64 blocks)."""
+    from knlp_b200 import routing
+    w = workloads.config("llama8b_b32_8k", dev)
+    kp, vp = w.planes()
+    S, Hq, d = w.query.shape
+    Hkv, nb = w.n_kv_heads, w.key_cache.shape[0]
+    rows = []
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        replay, _ = capture(torch, fn)
+        for _ in range(3):
+            replay()
+        torch.cuda.synchronize()
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+              for _ in range(steps)]
+        for a, b in ev:
+            a.record()
+            replay()
+            b.record()
+        torch.cuda.synchronize()
+        return [a.elapsed_time(b) for a, b in ev]
+
+    # unquantized K: bf16 N(0,1) rows in the workload's own pages
+    gen = torch.Generator(device=dev).manual_seed(3)
+    kfp = torch.randn(nb, PAGE, Hkv, d, device=dev, generator=gen).to(torch.bfloat16)
+    each = timed(lambda: ops.kfp16_vint4_decode(
+        w.query, kfp, w.value_cache, w.v_scales, w.block_table, w.seq_lens, Hkv, d,
+        v_zeros=w.v_zeros, asymmetric=True, max_seq_len=w.max_seq_len))
+    tok = int(sum(w.seq_lens_host)) * Hkv
+    byts = tok * (2 * d + d // 2 + (d // 32) * 4)
+    us = pct(each, 0.5) * 1e3
+    rows.append({"workload": "llama8b_b32_8k, K unquantized bf16 / V int4_asym (kfp16_vint4_decode)",
+                 "us_median": us, "algorithmic_bytes": byts,
+                 "tb_per_s": byts / us / 1e6, "frac": byts / us / 1e3 / peak_gbs, "steps": steps})
+    del kfp
+    # routed: 64 of each sequence's 512 blocks per kv head, drawn per head from the seed
+    k_sel = 64
+    prior = torch.rand(S, Hkv, w.block_table.shape[1], device=dev, generator=gen)
+    idx = prior.topk(k_sel, dim=-1).indices
+    tables = torch.gather(w.block_table[:, None, :].expand(-1, Hkv, -1).long(), 2, idx)
+    tables = tables.to(torch.int32).contiguous()
+    counts = torch.full((S, Hkv), k_sel, dtype=torch.int32, device=dev)
+    each = timed(lambda: routing.fused_routed_decode(w.query, kp, vp, nb, PAGE, Hkv, tables, counts))
+    byts = S * Hkv * k_sel * PAGE * w.kv_bytes_per_token_head()
+    us = pct(each, 0.5) * 1e3
+    rows.append({"workload": "llama8b_b32_8k, routed decode, 64 of 512 blocks per kv head",
+                 "us_median": us, "algorithmic_bytes": byts,
+                 "tb_per_s": byts / us / 1e6, "frac": byts / us / 1e3 / peak_gbs, "steps": steps})
+    return rows
+
+
+def run_write_path(args):
+    """Side measurement, not the headline: one JSON line per quantizer."""
+    import torch
+    from knlp_b200 import ops, workloads
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    for row in measure_write_path(torch, ops, workloads, dev, args.steps, args.warmup, args.scale):
+        print(json.dumps(row))
 
 
 def main():

@@ -29,6 +29,7 @@ multi-GPU context shard.
 
 from __future__ import annotations
 
+import contextlib
 import ctypes as C
 import os
 from typing import Optional, Tuple
@@ -81,7 +82,18 @@ def _stride2(t: torch.Tensor):
     return (C.c_int64 * 2)(t.stride(0), t.stride(1))
 
 
+_planes = {}  # (pointers, strides, dtype, mode) -> marshalled knlp_kv_plane
+
+
 def _plane(codes, scales, zeros, mode) -> _lib.KvPlane:
+    """The knlp_kv_plane of a cache.  A decode step passes the same tensors every time, so
+    the marshalled struct is kept per (pointers, strides, dtype, mode)."""
+    key = (codes.data_ptr(), scales.data_ptr(), 0 if zeros is None else zeros.data_ptr(), mode,
+           codes.stride(), scales.stride(), None if zeros is None else zeros.stride(),
+           codes.dtype)
+    p = _planes.get(key)
+    if p is not None:
+        return p
     p = _lib.KvPlane()
     if codes.dtype not in (torch.uint8, torch.int8):
         raise TypeError("code cache must be uint8 (INT4) or int8 (INT8)")
@@ -94,6 +106,9 @@ def _plane(codes, scales, zeros, mode) -> _lib.KvPlane:
     p.scales_stride = _stride3(scales)
     p.zeros_stride = _stride3(zeros) if zeros is not None else (C.c_int64 * 3)(0, 0, 0)
     p.mode = mode
+    if len(_planes) >= 4096:
+        _planes.clear()
+    _planes[key] = p
     return p
 
 
@@ -109,6 +124,14 @@ def _stream(dev) -> int:
     return torch.cuda.current_stream(dev).cuda_stream
 
 
+_SAME_DEVICE = contextlib.nullcontext()
+
+
+def _on(dev):
+    """Context that makes ``dev`` the current CUDA device (nothing to do when it already is)."""
+    return _SAME_DEVICE if torch.cuda.current_device() == dev.index else torch.cuda.device(dev)
+
+
 def _quant_append(key, value, k_plane, v_plane, slot_mapping, head_size, block_size, clip_ratio):
     src = key if key is not None else value
     dev = _need_cuda(key, value, slot_mapping)
@@ -121,7 +144,7 @@ def _quant_append(key, value, k_plane, v_plane, slot_mapping, head_size, block_s
     if slot_mapping.numel() != n_tokens:
         raise ValueError("slot_mapping length must equal the number of tokens")
     lib = _lib.load()
-    with torch.cuda.device(dev):
+    with _on(dev):
         rc = lib.knlp_b200_quant_append(
             key.data_ptr() if key is not None else None,
             _stride2(key) if key is not None else None,
@@ -271,7 +294,7 @@ def decode_partials(
     pl = torch.empty((S, Hq, n_splits), dtype=torch.float32, device=dev)
     po = torch.empty((S, Hq, n_splits, d), dtype=torch.float32, device=dev)
     lib = _lib.load()
-    with torch.cuda.device(dev):
+    with _on(dev):
         rc = lib.knlp_b200_decode_splitk(
             query.data_ptr(), _dt(query), _stride2(query), C.byref(k_plane), C.byref(v_plane),
             block_table.data_ptr(), block_table.stride(0), seq_lens.data_ptr(), num_blocks,
@@ -313,7 +336,7 @@ def combine_partials(pm: torch.Tensor, pl: torch.Tensor, po: torch.Tensor,
         om = torch.empty(rows_shape, dtype=torch.float32, device=dev)
         ol = torch.empty(rows_shape, dtype=torch.float32, device=dev)
         oo = torch.empty(rows_shape + (d,), dtype=torch.float32, device=dev)
-        with torch.cuda.device(dev):
+        with _on(dev):
             rc = lib.knlp_b200_combine(pm.data_ptr(), pl.data_ptr(), po.data_ptr(), n_parts,
                                        ml_row, ml_part, o_row, o_part, oo.data_ptr(), _lib.F32, d,
                                        om.data_ptr(), ol.data_ptr(), 1, n_rows, d, _stream(dev))
@@ -323,7 +346,7 @@ def combine_partials(pm: torch.Tensor, pl: torch.Tensor, po: torch.Tensor,
         out = torch.empty(rows_shape + (d,), dtype=out_dtype, device=dev)
     elif not out.is_contiguous() or out.numel() != n_rows * d:
         raise ValueError("out must be contiguous [..., d]")
-    with torch.cuda.device(dev):
+    with _on(dev):
         rc = lib.knlp_b200_combine(pm.data_ptr(), pl.data_ptr(), po.data_ptr(), n_parts,
                                    ml_row, ml_part, o_row, o_part, out.data_ptr(), _DT[out.dtype],
                                    d, None, None, 0, n_rows, d, _stream(dev))
@@ -344,7 +367,7 @@ def combine_to_packed(pm: torch.Tensor, pl: torch.Tensor, po: torch.Tensor) -> t
     n_rows = pm.numel() // max(n_parts, 1)
     packed = torch.empty(rows_shape + (d + 2,), dtype=torch.float32, device=dev)
     base = packed.data_ptr()
-    with torch.cuda.device(dev):
+    with _on(dev):
         rc = _lib.load().knlp_b200_combine(
             pm.data_ptr(), pl.data_ptr(), po.data_ptr(), n_parts, n_parts, 1, n_parts * d, d,
             base, _lib.F32, d + 2, base + 4 * d, base + 4 * (d + 1), d + 2, n_rows, d,
@@ -367,7 +390,7 @@ def combine_packed(gathered: torch.Tensor, out_dtype=torch.float32) -> torch.Ten
     out = torch.empty(rows_shape + (d,), dtype=out_dtype, device=dev)
     base = gathered.data_ptr()
     part = n_rows * (d + 2)
-    with torch.cuda.device(dev):
+    with _on(dev):
         rc = _lib.load().knlp_b200_combine(
             base + 4 * d, base + 4 * (d + 1), base, n_parts, d + 2, part, d + 2, part,
             out.data_ptr(), _DT[out.dtype], d, None, None, 0, n_rows, d, _stream(dev))
@@ -378,19 +401,29 @@ def combine_packed(gathered: torch.Tensor, out_dtype=torch.float32) -> torch.Ten
 _workspaces = {}  # (device index, stream) -> (float workspace, int32 counters left zero)
 
 
+_ws_sizes = {}  # shape -> (floats, counters) of knlp_b200_decode_workspace
+
+
 def _decode_workspace(dev: torch.device, S: int, Hq: int, Hkv: int, d: int, block_size: int,
                       max_seq_len: int):
     """Workspace of ``knlp_b200_decode_attention`` for the current stream: grown on demand,
     reused by every later call on that stream (calls on one stream are ordered)."""
-    nf, ni = C.c_int64(0), C.c_int64(0)
-    rc = _lib.load().knlp_b200_decode_workspace(S, Hq, Hkv, d, block_size, max_seq_len,
-                                                C.byref(nf), C.byref(ni))
-    _lib.check(rc, "knlp_b200_decode_workspace")
+    shape = (dev.index, S, Hq, Hkv, d, block_size, max_seq_len)
+    need = _ws_sizes.get(shape)
+    if need is None:
+        nf, ni = C.c_int64(0), C.c_int64(0)
+        with _on(dev):  # the size depends on the device's SM count
+            rc = _lib.load().knlp_b200_decode_workspace(S, Hq, Hkv, d, block_size, max_seq_len,
+                                                        C.byref(nf), C.byref(ni))
+        _lib.check(rc, "knlp_b200_decode_workspace")
+        if len(_ws_sizes) >= 4096:
+            _ws_sizes.clear()
+        need = _ws_sizes[shape] = (nf.value, ni.value)
     key = (dev.index, _stream(dev))
     cur = _workspaces.get(key)
-    if cur is None or cur[0].numel() < nf.value or cur[1].numel() < ni.value:
-        cur = (torch.empty(max(nf.value, 1 << 20), dtype=torch.float32, device=dev),
-               torch.zeros(max(ni.value, 4096), dtype=torch.int32, device=dev))
+    if cur is None or cur[0].numel() < need[0] or cur[1].numel() < need[1]:
+        cur = (torch.empty(max(need[0], 1 << 20), dtype=torch.float32, device=dev),
+               torch.zeros(max(need[1], 4096), dtype=torch.int32, device=dev))
         _workspaces[key] = cur
     return cur
 
@@ -456,7 +489,7 @@ def decode_attention(
         nt.key_stride, nt.value_stride = _stride2(new_key), _stride2(new_value)
         nt.dtype = _dt(new_key)
         nt.clip_ratio = float(OUTLIER_CLIP_RATIO if clip_ratio is None else clip_ratio)
-    with torch.cuda.device(dev):
+    with _on(dev):
         rc = _lib.load().knlp_b200_decode_append_attention(
             query.data_ptr(), _dt(query), _stride2(query), C.byref(k_plane), C.byref(v_plane),
             block_table.data_ptr(), block_table.stride(0), seq_lens.data_ptr(), num_blocks,

@@ -70,7 +70,7 @@ def fused_routed_decode(
     else:
         out = torch.empty((batch, n_heads, head_dim),
                           dtype=q.dtype if out_dtype is None else out_dtype, device=dev)
-    with torch.cuda.device(dev):
+    with ops._on(dev):
         rc = _lib.load().knlp_b200_routed_decode_attention(
             q.data_ptr(), ops._dt(q), ops._stride2(q), C.byref(k_plane), C.byref(v_plane),
             block_tables.data_ptr(), max_sel, block_counts.data_ptr(), num_blocks,
