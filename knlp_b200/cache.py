@@ -9,6 +9,9 @@ pieces here:
     _ensure_int4_cache            :2334-2480   the dedicated packed buffers and their
                                                per-block byte formula (:2451-2470)
     FusedInt4AttentionMetadata    :2078-2090   per-step metadata
+    FusedInt4AttentionBackend     :2096-2176   name, supported dtypes / head sizes, the
+                                               classes that belong together
+    FusedInt4AttentionMetadataBuilder :2182-2252  scheduler's common metadata -> per-step metadata
     do_kv_cache_update            :2483-2546   cache write of a step's new tokens
     _fused_decode                 :2851-2928   decode dispatch over k_precision / v_precision
 
@@ -75,6 +78,65 @@ class AttentionMetadata:
     seq_lens: torch.Tensor
     block_table: torch.Tensor
     slot_mapping: torch.Tensor
+
+
+class AttentionMetadataBuilder:
+    """Builds the per-step metadata from the scheduler's common metadata (reference
+    FusedInt4AttentionMetadataBuilder.build, :2210-2252): the fields are taken over as they
+    are; the FlashAttention scheduler metadata the reference pre-computes for its fp16-K
+    path has no use here.  ``common_attn_metadata`` is any object with the attributes
+    num_actual_tokens, max_query_len, query_start_loc, max_seq_len, seq_lens,
+    block_table_tensor and slot_mapping (vLLM's CommonAttentionMetadata has them)."""
+
+    # a decode step is one query token per sequence; such batches may be captured in a
+    # CUDA graph (reference _cudagraph_support = UNIFORM_SINGLE_TOKEN_DECODE)
+    reorder_batch_threshold = 1
+
+    def __init__(self, block_size: int, num_kv_heads: int, head_size: int, device=None):
+        self.block_size, self.num_kv_heads, self.head_size = block_size, num_kv_heads, head_size
+        self.device = device
+
+    def build(self, common_prefix_len: int, common_attn_metadata,
+              fast_build: bool = False) -> AttentionMetadata:
+        m = common_attn_metadata
+        return AttentionMetadata(
+            num_actual_tokens=m.num_actual_tokens, max_query_len=m.max_query_len,
+            query_start_loc=m.query_start_loc, max_seq_len=m.max_seq_len, seq_lens=m.seq_lens,
+            block_table=m.block_table_tensor, slot_mapping=m.slot_mapping)
+
+
+class AttentionBackend:
+    """What the serving engine asks a backend before it uses it (reference
+    FusedInt4AttentionBackend, :2096-2176), answered for this library's kernels."""
+
+    accept_output_buffer = True
+    forward_includes_kv_cache_update = False
+    supported_dtypes = [torch.float16, torch.bfloat16]
+    supported_kv_cache_dtypes = ["int4_fused"]
+
+    @staticmethod
+    def get_name() -> str:
+        return "FUSED_INT4"
+
+    @staticmethod
+    def get_builder_cls():
+        return AttentionMetadataBuilder
+
+    @staticmethod
+    def get_cache_cls():
+        return PackedKVCache
+
+    get_kv_cache_shape = staticmethod(get_kv_cache_shape)
+
+    @classmethod
+    def supports_kv_cache_dtype(cls, kv_cache_dtype) -> bool:
+        return kv_cache_dtype is None or kv_cache_dtype == "int4_fused"
+
+    @classmethod
+    def supports_head_size(cls, head_size: int) -> bool:
+        # the groups of 32 must tile the head (the tensor-core kernels take 64 and 128,
+        # other multiples of 32 run the stride-generic kernel)
+        return head_size > 0 and head_size % GROUP_SIZE == 0
 
 
 class PackedKVCache:

@@ -40,3 +40,30 @@ def test_bad_arguments():
         KC.PackedKVCache(8, 128, "int3", "int4")
     with pytest.raises(ValueError):
         KC.shadow_bytes_per_block(16, 8, 128, "int4", "fp16", False)
+
+
+def test_backend_facade_and_metadata_builder():
+    """Names and answers of the reference's backend class (:2096-2176) and the builder's
+    field-for-field hand-over (:2241-2251)."""
+    from types import SimpleNamespace
+    import torch
+    from knlp_b200 import cache as C
+    B = C.AttentionBackend
+    assert B.get_name() == "FUSED_INT4" and B.get_builder_cls() is C.AttentionMetadataBuilder
+    assert B.get_cache_cls() is C.PackedKVCache
+    assert B.supports_kv_cache_dtype(None) and B.supports_kv_cache_dtype("int4_fused")
+    assert not B.supports_kv_cache_dtype("fp8")
+    assert B.supports_head_size(128) and B.supports_head_size(96)
+    assert not B.supports_head_size(80) and not B.supports_head_size(0)
+    assert B.get_kv_cache_shape(10, 16, 8, 128) == (2, 10, 16, 8, 128)
+    assert torch.bfloat16 in B.supported_dtypes and not B.forward_includes_kv_cache_update
+    common = SimpleNamespace(num_actual_tokens=3, max_query_len=1,
+                             query_start_loc=torch.arange(4, dtype=torch.int32), max_seq_len=77,
+                             seq_lens=torch.tensor([5, 77, 20], dtype=torch.int32),
+                             block_table_tensor=torch.zeros(3, 5, dtype=torch.int32),
+                             slot_mapping=torch.tensor([4, 76, 19]), num_reqs=3)
+    meta = C.AttentionMetadataBuilder(16, 8, 128).build(0, common)
+    assert isinstance(meta, C.AttentionMetadata)
+    assert meta.max_seq_len == 77 and meta.num_actual_tokens == 3 and meta.max_query_len == 1
+    assert meta.seq_lens is common.seq_lens and meta.block_table is common.block_table_tensor
+    assert meta.slot_mapping is common.slot_mapping and meta.query_start_loc is common.query_start_loc
