@@ -293,6 +293,29 @@ int knlp_b200_routed_decode_attention(const void* query, int q_dtype, const int6
                                       unsigned flags, void* stream);
 
 /*
+ * Low-rank-V decode attention: the value side is stored as rank-r coefficients
+ * proj_i = B^T v_i with a per-head basis B, the weighted sum is taken in r dimensions and
+ * lifted once: out = B (sum_i softmax(q.k_i / sqrt(d))_i proj_i).  Same contract as
+ * lowrank_decode of the reference (pos_quant_v/kernel/vlowrank_kernel.py:139-156, kernel
+ * _lowrank_decode :25-75, which leaves the lift to a torch.bmm): all tensors contiguous,
+ *   query  [n_kv_heads, n_q_per_kv, head_dim]  fp16 or bf16 (qk_dtype), n_q_per_kv <= 8
+ *   key    [n_kv_heads, n_tokens, head_dim]    the same dtype, unquantized
+ *   proj   [n_kv_heads, n_tokens, rank]        fp32, rank = 32
+ *   basis  [n_kv_heads, head_dim, rank]        fp32
+ *   out    [n_kv_heads, n_q_per_kv, head_dim]  fp32; za_out (may be NULL): the coefficients
+ *          before the lift, [n_kv_heads, n_q_per_kv, rank] fp32
+ *   workspace: floats, >= what knlp_b200_lowrank_decode_workspace reports; scratch
+ * head_dim 64 or 128; 16-byte aligned bases.  Two launches (split-context kernel, finish);
+ * n_tokens = 0 gives zeros.
+ */
+int knlp_b200_lowrank_decode_workspace(int n_kv_heads, int n_q_per_kv, int n_tokens,
+                                       int64_t* workspace_floats_out);
+int knlp_b200_lowrank_decode(const void* query, const void* key, int qk_dtype, const float* proj,
+                             const float* basis, int n_kv_heads, int n_q_per_kv, int n_tokens,
+                             int head_dim, int rank, float* workspace, int64_t workspace_floats,
+                             float* za_out, float* out, void* stream);
+
+/*
  * Merge n_parts partials per (sequence, q head) row.  No counterpart function
  * in the reference: the algebra is its in-loop online-softmax recurrence
  * (:808-815, :883-887) applied across splits.

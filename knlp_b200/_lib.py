@@ -36,6 +36,8 @@ SYMBOLS = (
     "knlp_b200_decode_workspace",
     "knlp_b200_decode_append_attention",
     "knlp_b200_routed_decode_attention",
+    "knlp_b200_lowrank_decode_workspace",
+    "knlp_b200_lowrank_decode",
     "knlp_b200_combine",
     "knlp_b200_decode_noalloc",
     "knlp_b200_plugin_quantize",
@@ -126,6 +128,13 @@ def load() -> C.CDLL:
         C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
         C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int, C.c_int64,
         C.c_uint, C.c_void_p]
+    lib.knlp_b200_lowrank_decode_workspace.restype = C.c_int
+    lib.knlp_b200_lowrank_decode_workspace.argtypes = [C.c_int, C.c_int, C.c_int,
+                                                       C.POINTER(C.c_int64)]
+    lib.knlp_b200_lowrank_decode.restype = C.c_int
+    lib.knlp_b200_lowrank_decode.argtypes = [
+        C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
+        C.c_int, C.c_int, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]
     lib.knlp_b200_decode_workspace.restype = C.c_int
     lib.knlp_b200_decode_workspace.argtypes = [
         C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,

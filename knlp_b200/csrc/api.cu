@@ -367,6 +367,31 @@ int knlp_b200_routed_decode_attention(const void* query, int q_dtype, const int6
   return rc > 0 ? KNLP_ERR_STRIDE : rc;
 }
 
+int knlp_b200_lowrank_decode_workspace(int n_kv_heads, int n_q_per_kv, int n_tokens,
+                                       int64_t* workspace_floats_out) {
+  if (!workspace_floats_out) return KNLP_ERR_NULL;
+  if (n_kv_heads <= 0 || n_q_per_kv <= 0 || n_q_per_kv > 8 || n_tokens < 0) return KNLP_ERR_SHAPE;
+  *workspace_floats_out = lowrank_workspace_floats(n_kv_heads, n_q_per_kv, n_tokens, sm_count());
+  return KNLP_OK;
+}
+
+int knlp_b200_lowrank_decode(const void* query, const void* key, int qk_dtype, const float* proj,
+                             const float* basis, int n_kv_heads, int n_q_per_kv, int n_tokens,
+                             int head_dim, int rank, float* workspace, int64_t workspace_floats,
+                             float* za_out, float* out, void* stream) {
+  if (!query || !key || !proj || !basis || !workspace || !out) return KNLP_ERR_NULL;
+  if (qk_dtype != KNLP_F16 && qk_dtype != KNLP_BF16) return KNLP_ERR_DTYPE;
+  if (n_kv_heads <= 0 || n_kv_heads > 65535 || n_q_per_kv <= 0 || n_q_per_kv > 8 || n_tokens < 0)
+    return KNLP_ERR_SHAPE;
+  if ((head_dim != 64 && head_dim != 128) || rank != 32) return KNLP_ERR_SHAPE;
+  const uintptr_t al = reinterpret_cast<uintptr_t>(query) | reinterpret_cast<uintptr_t>(key) |
+                       reinterpret_cast<uintptr_t>(proj) | reinterpret_cast<uintptr_t>(basis);
+  if (al % 16) return KNLP_ERR_STRIDE;  // rows are copied and read in 16-byte pieces
+  return launch_lowrank_decode(query, key, qk_dtype, proj, basis, n_kv_heads, n_q_per_kv, n_tokens,
+                               head_dim, sm_count(), workspace, workspace_floats, za_out, out,
+                               static_cast<cudaStream_t>(stream));
+}
+
 int knlp_b200_combine(const float* part_m, const float* part_l, const float* part_o,
                       int n_parts, int64_t ml_row_stride, int64_t ml_part_stride,
                       int64_t o_row_stride, int64_t o_part_stride, void* out, int out_dtype,

@@ -133,6 +133,12 @@ int launch_decode_dq(const DecodeArgs& a, float* ws, int64_t ws_floats, int* int
                      const knlp_new_tokens* new_tokens, bool per_head_tables, cudaStream_t st);
 void dq_workspace_size(int n_seqs, int n_q_heads, int n_kv_heads, int head_dim, int n_sms,
                        int64_t* floats, int64_t* ints);
+// Low-rank-V decode (lowrank_decode.cu): split-context kernel + finish kernel.
+int launch_lowrank_decode(const void* q, const void* k, int qk_dtype, const float* proj,
+                          const float* basis, int n_kv_heads, int nq, int T, int head_dim,
+                          int n_sms, float* ws, int64_t ws_floats, float* za_out, float* out,
+                          cudaStream_t st);
+int64_t lowrank_workspace_floats(int n_kv_heads, int nq, int T, int n_sms);
 // Device-side status word of the decode kernels (0 = clean); synchronises.
 int read_and_clear_decode_status();
 

@@ -367,8 +367,42 @@ def gen_routed_cases(m, out):
         print("routed", name, "done", flush=True)
 
 
+def gen_lowrank_cases(out):
+    """Low-rank-V decode: the reference's own torch implementations ``lowrank_decode_ref`` and
+    ``dense_decode`` (pos_quant_v/kernel/vlowrank_kernel.py:157-174) on CPU tensors; the basis
+    is orthonormal (QR of a seeded matrix), the coefficients are proj = V B as the method
+    defines them."""
+    spec = importlib.util.spec_from_file_location(
+        "knlp_ref_vlowrank", os.path.join(REF, "pos_quant_v", "kernel", "vlowrank_kernel.py"))
+    m = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(m)
+    rec = {}
+    cases = (("gqa4_d128_bf16", 2, 4, 300, 128, "bf16"), ("gqa8_d64_f16", 3, 8, 70, 64, "f16"),
+             ("one_token_bf16", 1, 1, 1, 128, "bf16"), ("gqa5_d128_f16", 2, 5, 517, 128, "f16"))
+    for name, hkv, nq, T, dh, dt in cases:
+        g = torch.Generator().manual_seed(5100 + T + dh)
+        Q = torch.randn(hkv, nq, dh, generator=g).to(DT[dt])
+        K = (torch.randn(hkv, T, dh, generator=g) * 1.3).to(DT[dt])
+        V = torch.randn(hkv, T, dh, generator=g)
+        B = torch.linalg.qr(torch.randn(hkv, dh, 32, generator=g)).Q.contiguous()
+        proj = torch.bmm(V, B).contiguous()
+        rec[name + "_q"], rec[name + "_k"] = f16_bits(Q), f16_bits(K)  # raw 16-bit patterns
+        rec[name + "_proj"], rec[name + "_basis"] = proj.numpy(), B.numpy()
+        rec[name + "_out"] = m.lowrank_decode_ref(Q, K, proj, B).numpy()
+        rec[name + "_dense_of_lifted_v"] = m.dense_decode(Q, K, torch.bmm(proj, B.transpose(1, 2))).numpy()
+        rec[name + "_dtype"] = dt
+        print("lowrank", name, "done", flush=True)
+    out["lowrank"] = rec
+
+
 def main():
     out = {}
+    if "--only-lowrank" in sys.argv:
+        gen_lowrank_cases(out)
+        for name, rec in out.items():
+            np.savez_compressed(os.path.join(HERE, name + ".npz"), **rec)
+            print("saved", name)
+        return
     if "--only-routed" in sys.argv:
         gen_routed_cases(load_reference(), out)
         for name, rec in out.items():
