@@ -155,6 +155,64 @@ __device__ __forceinline__ void load_q_pairs(const void* base, int64_t row, int 
     }
 }
 
+// The weights of a pair's parts, w_p = l_p e^(m_p - m) / sum_q l_q e^(m_q - m), into
+// sw[row * tile + p] (parts <= 32; emit_partial: not normalised, and m and the sum go out
+// with the row).  Ends before the barrier that makes them visible.
+template <int HD>
+__device__ __forceinline__ void merge_weights(const float* pm, const float* pl, const int parts,
+                                              const int heads, float* sw, const int tile,
+                                              void* out, const int64_t out_row_stride,
+                                              const int64_t row0, const int emit_partial) {
+  const int tid = threadIdx.x;
+  // Four warps run here and nothing hides a round trip to L2 but more
+  // loads in flight, so the (row, part) pairs are spread over all 128 threads - thread =
+  // (part group j, row), rows fastest, so that the m / l loads of a part coalesce over
+  // its heads - every thread's loads are issued together, and the two reductions over
+  // the parts go through shared memory instead of dependent loads or shuffles.
+  int hp_log = 2;  // rows padded to a power of two, at least 4: at most 32 part groups
+  while ((1 << hp_log) < heads) ++hp_log;
+  const int hp = 1 << hp_log, n_grp = kThreads >> hp_log;
+  const int row = tid & (hp - 1), j = tid >> hp_log;
+  const bool row_ok = row < heads;
+  float* const red = sw + ((heads * tile + 3) & ~3);  // behind the weights
+  constexpr int kPer = 8;  // parts per thread: 32 parts over at least 4 groups
+  float lv[kPer], mv[kPer];
+#pragma unroll
+  for (int i = 0; i < kPer; ++i) {
+    const int p = j + i * n_grp;
+    const bool ok = row_ok && p < parts;
+    lv[i] = ok ? __ldcg(pl + p * heads + row) : 0.0f;
+    mv[i] = ok ? __ldcg(pm + p * heads + row) : -INFINITY;
+  }
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < kPer; ++i) mx = fmaxf(mx, lv[i] > 0.0f ? mv[i] : -INFINITY);
+  red[tid] = mx;
+  __syncthreads();
+  for (int g = 0; g < n_grp; ++g) mx = fmaxf(mx, red[(g << hp_log) + row]);
+  float sum = 0.0f;
+#pragma unroll
+  for (int i = 0; i < kPer; ++i) {
+    mv[i] = lv[i] > 0.0f ? __expf(mv[i] - mx) : 0.0f;
+    sum = fmaf(lv[i], mv[i], sum);
+  }
+  red[kThreads + tid] = sum;
+  __syncthreads();
+  sum = 0.0f;
+  for (int g = 0; g < n_grp; ++g) sum += red[kThreads + (g << hp_log) + row];
+  const float inv = emit_partial ? 1.0f : (sum > 0.0f ? 1.0f / sum : 0.0f);
+#pragma unroll
+  for (int i = 0; i < kPer; ++i) {
+    const int p = j + i * n_grp;
+    if (row_ok && p < parts) sw[row * tile + p] = mv[i] * inv;
+  }
+  if (emit_partial && j == 0 && row_ok) {
+    float* orow = static_cast<float*>(out) + (row0 + row) * out_row_stride;
+    orow[HD] = mx;
+    orow[HD + 1] = sum;
+  }
+}
+
 // Second half of merge_pair: a thread owns ITEMS (row, four elements) items and keeps
 // their sums; the partial outputs are fetched kBatch parts of every item at a time, all
 // those loads independent of each other (about 20 vector loads in flight per thread: the
@@ -234,6 +292,76 @@ __device__ __forceinline__ void merge_rows(const float* pm, const float* pl, con
   }
 }
 
+// The whole merge of a pair with at most 32 parts.  The first batch of partial outputs is
+// fetched BEFORE the weights are worked out (the loads do not depend on them), so its round
+// trip to L2 runs under the weights' own.
+template <int HD, int ITEMS>
+__device__ __forceinline__ void merge_one_pass(const float* pm, const float* pl, const float* po,
+                                               const int parts, const int heads, float* sw,
+                                               const int tile, void* out, const int out_dtype,
+                                               const int64_t out_row_stride, const int64_t row0,
+                                               const int emit_partial) {
+  const int tid = threadIdx.x;
+  constexpr int kVec = HD / 4;
+  constexpr int kBatch = ITEMS >= 10 ? 2 : 20 / ITEMS;
+  const int part4 = heads * kVec;  // float4 items of one part
+  const float4* po4 = reinterpret_cast<const float4*>(po) + tid;
+  float4 acc[ITEMS], v[ITEMS][kBatch];
+#pragma unroll
+  for (int k = 0; k < ITEMS; ++k) acc[k] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  auto fetch = [&](const int pb) {
+#pragma unroll
+    for (int q = 0; q < kBatch; ++q) {
+#pragma unroll
+      for (int k = 0; k < ITEMS; ++k) {
+        // a member that saw no token wrote zeros, so no value needs skipping
+        const bool valid = tid + k * kThreads < part4 && pb + q < parts;
+        v[k][q] = valid ? __ldcg(po4 + (static_cast<int64_t>(pb + q) * part4 + k * kThreads))
+                        : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      }
+    }
+  };
+  auto add = [&](const int pb) {
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const float* wr = sw + min((tid + k * kThreads) / kVec, heads - 1) * tile + pb;
+#pragma unroll
+      for (int q = 0; q < kBatch; ++q) {
+        const float wgt = pb + q < parts ? wr[q] : 0.0f;
+        acc[k].x = fmaf(v[k][q].x, wgt, acc[k].x);
+        acc[k].y = fmaf(v[k][q].y, wgt, acc[k].y);
+        acc[k].z = fmaf(v[k][q].z, wgt, acc[k].z);
+        acc[k].w = fmaf(v[k][q].w, wgt, acc[k].w);
+      }
+    }
+  };
+  fetch(0);
+  merge_weights<HD>(pm, pl, parts, heads, sw, tile, out, out_row_stride, row0, emit_partial);
+  __syncthreads();
+  add(0);
+  for (int pb = kBatch; pb < parts; pb += kBatch) {
+    fetch(pb);
+    add(pb);
+  }
+#pragma unroll
+  for (int k = 0; k < ITEMS; ++k) {
+    const int i = tid + k * kThreads;
+    if (i < part4) {
+      const int r = i / kVec, e4 = i % kVec;
+      const int64_t o = (row0 + r) * out_row_stride + 4 * e4;
+      if (emit_partial) {
+        float* orow = static_cast<float*>(out) + o;
+        orow[0] = acc[k].x; orow[1] = acc[k].y; orow[2] = acc[k].z; orow[3] = acc[k].w;
+      } else {
+        store_elem_rt(out, o, acc[k].x, out_dtype);
+        store_elem_rt(out, o + 1, acc[k].y, out_dtype);
+        store_elem_rt(out, o + 2, acc[k].z, out_dtype);
+        store_elem_rt(out, o + 3, acc[k].w, out_dtype);
+      }
+    }
+  }
+}
+
 // Merge of the partials of one pair by the CTA that arrived last: out[row] = sum_p w_p o_p
 // with w_p = l_p e^(m_p - m) / sum_q l_q e^(m_q - m).  pm, pl: [parts][heads]; po: [parts]
 // [heads][HD]; sw: shared-memory scratch of sw_floats floats; s_mrow, s_irow: MAXH floats
@@ -248,6 +376,24 @@ __device__ __noinline__ void merge_pair(const float* pm, const float* pl, const 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int tile = min(parts, sw_floats / heads);
   const bool one_pass = parts <= 32 && parts <= tile;
+  if (one_pass) {
+    const int n_items = (heads * (HD / 4) + kThreads - 1) / kThreads;
+    constexpr int kMaxItems = (MAXH * (HD / 4) + kThreads - 1) / kThreads;
+    if (n_items <= 1) {
+      merge_one_pass<HD, 1>(pm, pl, po, parts, heads, sw, tile, out, out_dtype, out_row_stride,
+                            row0, emit_partial);
+    } else if (n_items <= 2) {
+      merge_one_pass<HD, 2>(pm, pl, po, parts, heads, sw, tile, out, out_dtype, out_row_stride,
+                            row0, emit_partial);
+    } else if (n_items <= 4 || kMaxItems <= 4) {
+      merge_one_pass<HD, 4>(pm, pl, po, parts, heads, sw, tile, out, out_dtype, out_row_stride,
+                            row0, emit_partial);
+    } else {
+      merge_one_pass<HD, kMaxItems>(pm, pl, po, parts, heads, sw, tile, out, out_dtype,
+                                    out_row_stride, row0, emit_partial);
+    }
+    return;
+  }
   {
     constexpr int kRowsW = MAXH / kWarpsCta;
     float rm[kRowsW], rl[kRowsW], lp[kRowsW], mp[kRowsW];
