@@ -71,7 +71,9 @@ typedef enum {
   /* Unquantized K plane of the hybrid decodes (reference kfp16_vint4_decode :1159-1224,
    * kfp16_vint8_decode :1975-2028): codes points to [.., head_size] fp16 or bf16 values,
    * codes_stride counts those 2-byte elements, scales / zeros are unused (may be NULL).
-   * Decode only, K side only; runs on the stride-generic kernel. */
+   * Decode only, K side only.  knlp_b200_decode_attention runs it on the tensor cores (head_dim
+   * 64 / 128, heads of a token adjacent in memory, 16-byte aligned rows); the split-context
+   * entry points and other layouts run the stride-generic kernel. */
   KNLP_KV_F16 = 4,
   KNLP_KV_BF16 = 5
 } knlp_kv_mode;

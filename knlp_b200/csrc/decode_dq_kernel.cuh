@@ -25,6 +25,12 @@
 // The merge of a pair's partials is done by the member that arrives last (counted with
 // an atomic after a fence), straight into the output; with many members per pair the
 // host asks for the partials only and runs the combine kernel on them.
+//
+// Variants of the same kernel: K modes INT4 (sym / asym), INT8 and unquantized fp16 / bf16
+// (the K tile is then the MMA's A operand as it lies in memory, bf16 through the bf16 MMA
+// with q split into two bf16 parts); V modes INT4 and INT8; the step's new token appended
+// by the pair's last member (append_token); per-kv-head page tables for routed decode
+// (instantiation ROUTED: one kv head per CTA, scale rows fetched per (token, head)).
 
 #pragma once
 
