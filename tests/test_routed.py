@@ -116,3 +116,42 @@ def test_select_top_k_blocks(cuda_device):
     assert torch.equal(tables, torch.topk(prior, 6, dim=-1).indices)
     tables, counts = routing.select_top_k_blocks(prior, 50)
     assert tables.shape == (3, 4, 20) and int(counts.max()) == 20
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("k_mode,v_mode", [("int8", "int4_asym"), ("int8", "int8"),
+                                           ("int4_sym", "int4_sym"), ("fp16", "int4_asym"),
+                                           ("bf16", "int8")])
+def test_routed_other_modes_equal_dense(k_mode, v_mode, cuda_device):
+    """Every K / V mode pair of the dense kernel also runs with per-kv-head block tables:
+    selecting all blocks of a sequence in order reproduces the dense decode."""
+    from knlp_b200 import _lib, ops, routing, workloads
+    fp = k_mode in ("fp16", "bf16")
+    w = workloads.build("routed_modes", n_seqs=4, n_q_heads=8, n_kv_heads=2, head_dim=128,
+                        seq_lens=[16 * 21, 16 * 5, 16 * 64, 16], device=cuda_device, seed=23,
+                        shuffle_pages=True, v_mode=v_mode,
+                        k_mode=k_mode if not fp else ("int8" if v_mode == "int8" else "int4_asym"))
+    kp, vp = w.planes()
+    nb, P = w.key_cache.shape[0], 16
+    if fp:  # an unquantized K cache of its own in the same pages
+        g = torch.Generator(device=cuda_device).manual_seed(3)
+        kfp = torch.randn(nb, P, 2, 128, device=cuda_device, generator=g).to(
+            torch.float16 if k_mode == "fp16" else torch.bfloat16)
+        kp = ops._fp_plane(kfp)
+    dense = ops.decode_attention(w.query, kp, vp, nb, w.block_table, w.seq_lens, 2, 128, P,
+                                 out_dtype=torch.float32)
+    tables = w.block_table[:, None, :].expand(-1, 2, -1).contiguous()
+    counts = (w.seq_lens // P)[:, None].expand(-1, 2).contiguous().to(torch.int32)
+    routed = routing.fused_routed_decode(w.query, kp, vp, nb, P, 2, tables, counts,
+                                         out_dtype=torch.float32)
+    torch.testing.assert_close(routed, dense, rtol=2e-4, atol=2e-5)
+    # a different selection per head: only the first half of the blocks for head 1
+    counts2 = counts.clone()
+    counts2[:, 1] = torch.clamp(counts[:, 1] // 2, min=1)
+    routed2 = routing.fused_routed_decode(w.query, kp, vp, nb, P, 2, tables, counts2,
+                                          out_dtype=torch.float32)
+    half = ops.decode_attention(w.query, kp, vp, nb, w.block_table,
+                                (counts2[:, 1] * P).contiguous(), 2, 128, P,
+                                out_dtype=torch.float32)
+    torch.testing.assert_close(routed2[:, :4], dense[:, :4], rtol=2e-4, atol=2e-5)
+    torch.testing.assert_close(routed2[:, 4:], half[:, 4:], rtol=2e-4, atol=2e-5)
