@@ -274,7 +274,8 @@ int knlp_b200_decode_append_attention(const void* query, int q_dtype, const int6
  *   block_tables  int32, row s * n_kv_heads + h (row stride bt_stride elements) lists the
  *                 selected physical blocks of kv head h of sequence s
  *   block_counts  int32 [n_seqs * n_kv_heads]: valid entries of each row (0: the q heads
- *                 of that kv head get zeros, as in the reference)
+ *                 of that kv head get zeros, as in the reference; counts above
+ *                 max_selected_blocks are cut there, as the reference's loop bound does)
  *   query         [n_seqs, n_q_heads, head_dim], q_stride[0] == n_q_heads * q_stride[1]
  *   workspace / counters: as knlp_b200_decode_attention, sized by
  *                 knlp_b200_decode_workspace(n_seqs * n_kv_heads, n_q_heads / n_kv_heads, 1,
@@ -307,8 +308,8 @@ int knlp_b200_routed_decode_attention(const void* query, int q_dtype, const int6
  *   out    [n_kv_heads, n_q_per_kv, head_dim]  fp32; za_out (may be NULL): the coefficients
  *          before the lift, [n_kv_heads, n_q_per_kv, rank] fp32
  *   workspace: floats, >= what knlp_b200_lowrank_decode_workspace reports; scratch
- * head_dim 64 or 128; 16-byte aligned bases.  Two launches (split-context kernel, finish);
- * n_tokens = 0 gives zeros.
+ * head_dim 64 or 128; 16-byte aligned bases; n_tokens >= 1.  Two launches (split-context
+ * kernel, finish).
  */
 int knlp_b200_lowrank_decode_workspace(int n_kv_heads, int n_q_per_kv, int n_tokens,
                                        int64_t* workspace_floats_out);

@@ -381,7 +381,7 @@ int knlp_b200_lowrank_decode(const void* query, const void* key, int qk_dtype, c
                              float* za_out, float* out, void* stream) {
   if (!query || !key || !proj || !basis || !workspace || !out) return KNLP_ERR_NULL;
   if (qk_dtype != KNLP_F16 && qk_dtype != KNLP_BF16) return KNLP_ERR_DTYPE;
-  if (n_kv_heads <= 0 || n_kv_heads > 65535 || n_q_per_kv <= 0 || n_q_per_kv > 8 || n_tokens < 0)
+  if (n_kv_heads <= 0 || n_kv_heads > 65535 || n_q_per_kv <= 0 || n_q_per_kv > 8 || n_tokens < 1)
     return KNLP_ERR_SHAPE;
   if ((head_dim != 64 && head_dim != 128) || rank != 32) return KNLP_ERR_SHAPE;
   const uintptr_t al = reinterpret_cast<uintptr_t>(query) | reinterpret_cast<uintptr_t>(key) |

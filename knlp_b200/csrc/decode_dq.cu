@@ -80,6 +80,7 @@ int launch_decode_dq(const DecodeArgs& a_in, float* ws, int64_t ws_floats, int* 
                      int64_t n_ints, int max_seq_len, bool emit_partial, int n_sms,
                      const knlp_new_tokens* nt, bool per_head_tables, cudaStream_t st) {
   DqParams dp{};
+  dp.len_cap = 0x7fffffff;
   if (decode_mma_layout(a_in, &dp.hpb_log2, &dp.page_log2)) return 1;
   DecodeArgs a = a_in;
   if (per_head_tables) {
@@ -90,7 +91,7 @@ int launch_decode_dq(const DecodeArgs& a_in, float* ws, int64_t ws_floats, int* 
     if (a.q_stride[0] != static_cast<int64_t>(a.n_q_heads) * a.q_stride[1]) return 1;
     if (static_cast<int64_t>(a.n_seqs) * a.n_kv_heads > 0x7fffffff) return 1;
     dp.vheads = a.n_kv_heads;
-    dp.len_shift = dp.page_log2;
+    dp.len_cap = max_seq_len;  // = the blocks a table row holds: larger counts are cut there
     dp.hpb_log2 = 0;
     a.n_seqs *= a.n_kv_heads;
     a.n_q_heads = n_rep;

@@ -65,10 +65,10 @@ struct DqParams {
   // Per-kv-head page tables (routed decode).  vheads > 0: the launch sees every (sequence,
   // kv head) as a sequence of its own with ONE kv head - row v of block_table / seq_lens /
   // query / out belongs to kv head v % vheads of a cache that holds vheads heads per token
-  // (heads per CTA is 1 then).  len_shift: seq_lens count 1 << len_shift tokens each
-  // (lengths given in whole blocks).
+  // (heads per CTA is 1 then), seq_lens count whole blocks, and lengths are cut at len_cap
+  // tokens (a table row holds no more blocks).
   int vheads;
-  int len_shift;
+  int len_cap;
 };
 
 namespace {
@@ -635,7 +635,8 @@ decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
   // a sequence without cached tokens still has work when the step appends one to it
   const bool appending = dp.new_key != nullptr;
   auto seq_chunks = [&](int s) -> int {
-    const int L = __ldg(a.seq_lens + s) << dp.len_shift;
+    const int L = ROUTED ? min(__ldg(a.seq_lens + s) << dp.page_log2, dp.len_cap)
+                         : __ldg(a.seq_lens + s);
     if (L < 0 || (L == 0 && !appending)) return 0;
     return L > CT ? (L + CT - 1) / CT : 1;
   };
@@ -809,7 +810,8 @@ decode_dq_kernel(const DecodeArgs a, const DqParams dp) {
     const int parts = parts_in;
     int* const ticket = dp.counters + (seq * HBn + hb);
     const int kvh = hb * HPB + w_head;
-    const int len = __ldg(a.seq_lens + seq) << dp.len_shift;
+    const int len = ROUTED ? min(__ldg(a.seq_lens + seq) << dp.page_log2, dp.len_cap)
+                           : __ldg(a.seq_lens + seq);
     const int32_t* bt_row = a.block_table + static_cast<int64_t>(seq) * a.bt_stride;
     const int hmem = hb + (routed ? seq % dp.vheads : 0);  // head block within the cache
     const int dyn0 = 2 * n_static;  // chunk of ticket 0

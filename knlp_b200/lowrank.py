@@ -41,6 +41,10 @@ def lowrank_decode(Q: torch.Tensor, K: torch.Tensor, proj: torch.Tensor, Bbasis:
         raise TypeError("proj and Bbasis must be float32")
     if r != 32 or dh not in (64, 128) or nq > 8:
         raise NotImplementedError("built for rank 32, head_dim 64 / 128, at most 8 queries per head")
+    if T == 0:  # no token to attend to
+        o = torch.zeros((Hkv, nq, dh), dtype=torch.float32, device=dev)
+        return (o, torch.zeros((Hkv, nq, r), dtype=torch.float32, device=dev)) \
+            if return_coefficients else o
     Q, K, proj, Bbasis = (t if t.is_contiguous() else t.contiguous() for t in (Q, K, proj, Bbasis))
     lib = _lib.load()
     need = C.c_int64(0)

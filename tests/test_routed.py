@@ -155,3 +155,10 @@ def test_routed_other_modes_equal_dense(k_mode, v_mode, cuda_device):
                                 out_dtype=torch.float32)
     torch.testing.assert_close(routed2[:, :4], dense[:, :4], rtol=2e-4, atol=2e-5)
     torch.testing.assert_close(routed2[:, 4:], half[:, 4:], rtol=2e-4, atol=2e-5)
+    # counts beyond the table's width are cut at the width, as the reference's loop does
+    short = tables[:, :, :3].contiguous()
+    over = routing.fused_routed_decode(w.query, kp, vp, nb, P, 2, short,
+                                       torch.full_like(counts, 50), out_dtype=torch.float32)
+    exact = routing.fused_routed_decode(w.query, kp, vp, nb, P, 2, short,
+                                        torch.full_like(counts, 3), out_dtype=torch.float32)
+    torch.testing.assert_close(over, exact, rtol=2e-4, atol=2e-5)
