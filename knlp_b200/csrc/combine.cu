@@ -38,7 +38,8 @@ combine_kernel(const float* __restrict__ pm, const float* __restrict__ pl,
   // global maximum over the non-empty parts
   float m = -INFINITY;
   for (int p = threadIdx.x; p < n_parts; p += kThreads) {
-    if (rl[p * ml_part] > 0.0f) m = fmaxf(m, rm[p * ml_part]);
+    const float lp = rl[p * ml_part], mp = rm[p * ml_part];  // both loads issued at once
+    m = fmaxf(m, lp > 0.0f ? mp : -INFINITY);
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
@@ -53,15 +54,22 @@ combine_kernel(const float* __restrict__ pm, const float* __restrict__ pl,
   float acc[kMaxEpl];
 #pragma unroll
   for (int i = 0; i < kMaxEpl; ++i) acc[i] = 0.0f;
+  // every load of a part is issued whatever its weight turns out to be (a value of an
+  // empty part is dropped by the select, not by skipping its load): no load waits for
+  // another, and four parts are in flight per warp
 #pragma unroll 4
   for (int p = warp; p < n_parts; p += kWarps) {
     const float lp = rl[p * ml_part];
-    const float w = lp > 0.0f ? __expf(rm[p * ml_part] - m) : 0.0f;
-    l += lp * w;
+    const float mp = rm[p * ml_part];
     const float* src = ro + p * o_part + lane * epl;
+    float v[kMaxEpl];
+#pragma unroll
+    for (int i = 0; i < kMaxEpl; ++i) v[i] = i < epl ? src[i] : 0.0f;
+    const float w = lp > 0.0f ? __expf(mp - m) : 0.0f;
+    l += lp * w;
 #pragma unroll
     for (int i = 0; i < kMaxEpl; ++i)
-      if (i < epl) acc[i] = fmaf(w > 0.0f ? src[i] : 0.0f, w, acc[i]);
+      if (i < epl) acc[i] = fmaf(w > 0.0f ? v[i] : 0.0f, w, acc[i]);
   }
   if (lane == 0) s_l[warp] = l;
 #pragma unroll
@@ -116,8 +124,10 @@ combine_pairs_kernel(const float* __restrict__ ws_m, const float* __restrict__ w
   __shared__ float s_o[kWarps][32];
 
   float m = -INFINITY;
-  for (int p = threadIdx.x; p < parts; p += kThreads)
-    if (rl[p * heads] > 0.0f) m = fmaxf(m, rm[p * heads]);
+  for (int p = threadIdx.x; p < parts; p += kThreads) {
+    const float lp = __ldcg(rl + p * heads), mp = __ldcg(rm + p * heads);
+    m = fmaxf(m, lp > 0.0f ? mp : -INFINITY);
+  }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
   if (lane == 0) s_red[warp] = m;
@@ -126,15 +136,17 @@ combine_pairs_kernel(const float* __restrict__ ws_m, const float* __restrict__ w
 #pragma unroll
   for (int w = 1; w < kWarps; ++w) m = fmaxf(m, s_red[w]);
 
+  // all three loads of a part are issued unconditionally and eight parts at a time: with
+  // four warps on the SM only loads in flight hide the round trips to L2
   float l = 0.0f, acc = 0.0f;
-#pragma unroll 4
+#pragma unroll 8
   for (int p = warp; p < parts; p += kWarps) {
-    const float lp = rl[p * heads];
-    if (lp > 0.0f) {
-      const float w = __expf(rm[p * heads] - m);
-      l = fmaf(lp, w, l);
-      acc = fmaf(ro[p * o_part], w, acc);
-    }
+    const float lp = __ldcg(rl + p * heads);
+    const float mp = __ldcg(rm + p * heads);
+    const float op = __ldcg(ro + p * o_part);
+    const float w = lp > 0.0f ? __expf(mp - m) : 0.0f;
+    l = fmaf(lp, w, l);
+    acc = fmaf(lp > 0.0f ? op : 0.0f, w, acc);
   }
   if (lane == 0) s_l[warp] = l;
   s_o[warp][lane] = acc;
