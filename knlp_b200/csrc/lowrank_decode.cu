@@ -233,16 +233,19 @@ lowrank_finish_kernel(const float* __restrict__ part_m, const float* __restrict_
   const float* po = part_o + static_cast<int64_t>(row) * n_splits * kLrRank;
   // the row's maximum (every warp computes it), then each warp sums a quarter of the splits
   float m = -INFINITY;
-  for (int p = lane; p < n_splits; p += 32) m = fmaxf(m, pl[p] > 0.0f ? pm[p] : -INFINITY);
+  for (int p = lane; p < n_splits; p += 32) {
+    const float lp = pl[p], mp = pm[p];
+    m = fmaxf(m, lp > 0.0f ? mp : -INFINITY);
+  }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
   float l = 0.0f, z = 0.0f;
 #pragma unroll 4
   for (int p = warp; p < n_splits; p += kWarpsCta) {
-    const float lp = pl[p];
-    const float f = lp > 0.0f ? __expf(pm[p] - m) : 0.0f;
+    const float lp = pl[p], mp = pm[p], zp = po[p * kLrRank + lane];  // issued together
+    const float f = lp > 0.0f ? __expf(mp - m) : 0.0f;
     l = fmaf(lp, f, l);
-    z = fmaf(po[p * kLrRank + lane], f, z);
+    z = fmaf(lp > 0.0f ? zp : 0.0f, f, z);
   }
   s_wz[warp][lane] = z;
   if (lane == 0) s_wl[warp] = l;
