@@ -97,6 +97,31 @@ def test_argument_errors_are_reported_on_the_host(lib):
     assert lib.knlp_b200_combine(p, p, p, 1, 1, 1, 1, 1, p, 1, 1, p, p, 1, 1, 64, null) == -3
 
 
+def test_host_side_checks_of_the_routed_and_lowrank_entry_points(lib):
+    """Argument errors are found on the host, before anything is launched."""
+    from knlp_b200 import _lib
+    null = None
+    p = C.c_void_p(0x1000)
+    st2 = (C.c_int64 * 2)(128, 128)
+    pk = _lib.KvPlane(); pk.codes = p.value; pk.scales = p.value; pk.mode = _lib.KV_INT4_SYM
+    R = lib.knlp_b200_routed_decode_attention
+    args = lambda out, flags, max_sel: (p, 2, st2, C.byref(pk), C.byref(pk), p, 4, p, 8, 1, 4, 1, 128,
+                                        16, max_sel, p, 1 << 20, p, 64, out, 2, 128, flags, null)
+    assert R(*args(null, 0, 4)) == -1            # no output
+    assert R(*args(p, 8, 4)) == -4               # fixed splits have no per-head tables
+    assert R(*args(p, 0, -1)) == -2
+    L = lib.knlp_b200_lowrank_decode
+    assert L(null, p, 2, p, p, 1, 1, 8, 128, 32, p, 1 << 20, null, p, null) == -1
+    assert L(p, p, 0, p, p, 1, 1, 8, 128, 32, p, 1 << 20, null, p, null) == -3   # fp32 q / K
+    assert L(p, p, 2, p, p, 1, 9, 8, 128, 32, p, 1 << 20, null, p, null) == -2   # > 8 queries
+    assert L(p, p, 2, p, p, 1, 1, 8, 128, 16, p, 1 << 20, null, p, null) == -2   # rank != 32
+    assert L(p, p, 2, p, p, 1, 1, 0, 128, 32, p, 1 << 20, null, p, null) == -2   # no token
+    assert L(C.c_void_p(0x1004), p, 2, p, p, 1, 1, 8, 128, 32, p, 1 << 20, null, p, null) == -5
+    n = C.c_int64(0)
+    assert lib.knlp_b200_lowrank_decode_workspace(1, 9, 8, C.byref(n)) == -2
+    assert lib.knlp_b200_lowrank_decode_workspace(1, 1, 8, null) == -1
+
+
 def test_decode_plan_fills_waves(lib):
     n = C.c_int(0)
     ws = C.c_int64(0)
