@@ -5,7 +5,7 @@
 // proj [Hkv, T, r] fp32, basis [Hkv, dh, r] fp32, out [Hkv, nq, dh] fp32.
 //
 // Two launches.  (1) lowrank_splitk_kernel: grid (split, kv head); a CTA streams its token
-// range through shared memory in 64-token stages (cp.async, three stages), the scores of
+// range through shared memory in 64-token stages (cp.async, two stages, four CTAs per SM), the scores of
 // a 16-token tile are one ldmatrix + one m16n8k16 MMA per 16 elements of the head
 // dimension with the head's queries as the B columns (the K tile is the A operand as it
 // lies in memory, as in the unquantized-K mode of the paged decode kernel), the softmax is
@@ -25,7 +25,7 @@ namespace {
 
 constexpr int kLrRank = 32;             // coefficients per token: one per lane
 constexpr int kLrStageTok = 64;         // tokens per stage: one 16-token tile per warp
-constexpr int kLrStages = 3;
+constexpr int kLrStages = 2;
 
 template <int DH>
 struct LrGeo {
@@ -303,10 +303,10 @@ int launch_lr(const void* q, const void* k, const float* proj, int n_kv_heads, i
 
 }  // namespace
 
-// Split count: as many CTAs as the machine holds at once (three fit an SM; two and four
-// times as many measured slower), no split below 256 tokens.
+// Split count: as many CTAs as the machine holds at once (four fit an SM; twice and four
+// times as many, smaller splits measured slower), no split below 256 tokens.
 int lowrank_plan(int n_kv_heads, int T, int n_sms, int* chunk_out) {
-  int n = 3 * n_sms / n_kv_heads;
+  int n = 4 * n_sms / n_kv_heads;
   const int cap = (T + 255) / 256;
   if (n > cap) n = cap;
   if (n < 1) n = 1;
