@@ -832,7 +832,33 @@ def measure_side_kernels(torch, ops, workloads, dev, steps, peak_gbs):
     rows.append({"workload": "llama8b_b32_8k, routed decode, 64 of 512 blocks per kv head",
                  "us_median": us, "algorithmic_bytes": byts,
                  "tb_per_s": byts / us / 1e6, "frac": byts / us / 1e3 / peak_gbs, "steps": steps})
+    del w, kp, vp, tables, counts, prior, idx
+    torch.cuda.empty_cache()
+    # low-rank-V decode: 8 kv heads x 131072 tokens, bf16 K, rank-32 fp32 coefficients
+    from knlp_b200 import lowrank
+    hkv, nq, T, dh = 8, 4, 131072, 128
+    Q = torch.randn(hkv, nq, dh, device=dev, generator=gen).to(torch.bfloat16)
+    K = torch.randn(hkv, T, dh, device=dev, generator=gen).to(torch.bfloat16)
+    proj = torch.randn(hkv, T, 32, device=dev, generator=gen)
+    basis = torch.linalg.qr(torch.randn(hkv, dh, 32, device=dev, generator=gen)).Q.contiguous()
+    each = timed(lambda: lowrank.lowrank_decode(Q, K, proj, basis))
+    byts = hkv * T * (2 * dh + 4 * 32)
+    us = pct(each, 0.5) * 1e3
+    rows.append({"workload": "low-rank-V decode, 8 kv heads x 131072 tokens, bf16 K + rank-32 fp32",
+                 "us_median": us, "algorithmic_bytes": byts,
+                 "tb_per_s": byts / us / 1e6, "frac": byts / us / 1e3 / peak_gbs, "steps": steps})
     return rows
+
+
+def run_side_kernels(args):
+    """Side measurement: the decode variants beside the headline, one JSON line each."""
+    import torch
+    from knlp_b200 import ops, workloads
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    peak_gbs, _ = peaks()
+    for row in measure_side_kernels(torch, ops, workloads, dev, max(args.steps, 3), peak_gbs):
+        print(json.dumps(row), flush=True)
 
 
 def run_write_path(args):
@@ -864,10 +890,16 @@ def main():
                     help="end-to-end leg as eager operator calls instead of one replayed CUDA graph")
     ap.add_argument("--append-loop", action="store_true",
                     help="time 64 append+attend steps of --workload, append separate and fused")
+    ap.add_argument("--side-kernels", action="store_true",
+                    help="time the decode variants beside the headline (unquantized K, routed, "
+                         "low-rank V) and print one JSON line each")
     ap.add_argument("--write-path", action="store_true",
                     help="time the quantize-and-append kernel instead (side measurement)")
     args = ap.parse_args()
     shape_of(args.workload)  # unknown workloads are refused up front
+    if args.side_kernels:
+        run_side_kernels(args)
+        return
     if args.write_path:
         run_write_path(args)
     elif args.append_loop:
