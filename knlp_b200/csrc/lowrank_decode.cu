@@ -72,26 +72,45 @@ lowrank_splitk_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict
     }
   }
 
-  // ---- copies of one stage: K rows swizzled for ldmatrix, proj rows as they are
+  // ---- copies of one stage: K rows swizzled for ldmatrix, proj rows as they are.  A
+  // thread's pieces of a stage lie a fixed distance apart (8 K rows, 16 coefficient rows),
+  // so a full stage costs one address per plane and immediate offsets.
+  constexpr int kKPer = kLrStageTok * G::kKCh / kThreads;  // K pieces per thread and stage
+  constexpr int kKRowStep = kThreads / G::kKCh;            // rows between them
+  constexpr int kPPer = kLrStageTok * 8 / kThreads;        // coefficient pieces (8 per row)
+  const int k_row = tid / G::kKCh, k_col = tid % G::kKCh;
+  const int p_row = tid >> 3, p_col = tid & 7;
+  const uint32_t k_dst = k_row * G::kKRow + ((k_col ^ (k_row & 7)) << 4);  // row & 7 survives + 8i
+  const uint32_t p_dst = G::kOffP + p_row * 128 + p_col * 16;
+  const uint8_t* const k_src = kh + (static_cast<int64_t>(k_row) * G::kKRow + k_col * 16);
+  const float* const p_src = ph + (p_row * kLrRank + p_col * 4);
+  static_assert(kKRowStep % 8 == 0, "the swizzle of a thread's pieces must not change");
   auto fill = [&](const int c, const int slot) {
     const int tok0 = t0 + c * kLrStageTok;
     const uint32_t base = smem_base + slot * G::kStageBytes;
-    if (tok0 < t1) {
+    if (tok0 + kLrStageTok <= t1) {  // a full stage: no predicates
+      const uint8_t* ks = k_src + static_cast<int64_t>(tok0) * G::kKRow;
+      const float* ps = p_src + static_cast<int64_t>(tok0) * kLrRank;
 #pragma unroll
-      for (int i = 0; i < kLrStageTok * G::kKCh / kThreads; ++i) {
-        const int piece = tid + i * kThreads;
-        const int row = piece / G::kKCh, col = piece % G::kKCh;
+      for (int i = 0; i < kKPer; ++i)
+        cp_async16(base + k_dst + i * kKRowStep * G::kKRow, ks + i * kKRowStep * G::kKRow, 16);
+#pragma unroll
+      for (int i = 0; i < kPPer; ++i)
+        cp_async16(base + p_dst + i * 16 * 128, ps + i * 16 * kLrRank, 16);
+    } else if (tok0 < t1) {
+#pragma unroll
+      for (int i = 0; i < kKPer; ++i) {
+        const int row = k_row + i * kKRowStep;
         const bool live = tok0 + row < t1;
-        const uint8_t* src = kh + (static_cast<int64_t>(tok0 + row) * G::kKRow + col * 16);
-        cp_async16(base + row * G::kKRow + ((col ^ (row & 7)) << 4), live ? src : kh, live ? 16 : 0);
+        const uint8_t* src = k_src + static_cast<int64_t>(tok0 + i * kKRowStep) * G::kKRow;
+        cp_async16(base + k_dst + i * kKRowStep * G::kKRow, live ? src : kh, live ? 16 : 0);
       }
 #pragma unroll
-      for (int i = 0; i < kLrStageTok * 8 / kThreads; ++i) {
-        const int piece = tid + i * kThreads;
-        const int row = piece >> 3, col = piece & 7;
+      for (int i = 0; i < kPPer; ++i) {
+        const int row = p_row + i * 16;
         const bool live = tok0 + row < t1;
-        const float* src = ph + (static_cast<int64_t>(tok0 + row) * kLrRank + col * 4);
-        cp_async16(base + G::kOffP + row * 128 + col * 16, live ? src : ph, live ? 16 : 0);
+        const float* src = p_src + static_cast<int64_t>(tok0 + i * 16) * kLrRank;
+        cp_async16(base + p_dst + i * 16 * 128, live ? src : ph, live ? 16 : 0);
       }
     }
     cp_async_commit();
